@@ -30,11 +30,28 @@ enum {
     TI_SEQ_MIXER_HGRN2 = 3,     /* the same recurrence with the forget gate f as decay and 1 - f as the written key */
     TI_SEQ_MIXER_LATENT = 4     /* softmax attention whose keys / values are linear images of a cached low-rank vector + one shared rotated key part */
 };
-enum { TI_SEQ_ACT_RELU = 0, TI_SEQ_ACT_SILU = 1, TI_SEQ_ACT_GELU_TANH = 2 };
+enum {
+    TI_SEQ_ACT_RELU = 0, TI_SEQ_ACT_SILU = 1, TI_SEQ_ACT_GELU_TANH = 2,
+    TI_SEQ_ACT_XIELU = 3 /* a z^2 + z / 2 for z > 0, b (exp(z) - 1 - z) + z / 2 otherwise; a = softplus(act[0]), b = 1/2 + softplus(act[1]) */
+};
 enum {
     TI_SEQ_FF_GLU = 0,      /* down(act(gate h) * up h) */
     TI_SEQ_FF_POLYNORM = 1, /* down(a N(z) + b N(z^2) + c N(z^3) + e), z = up h, N = division by the RMS over the inner size */
-    TI_SEQ_FF_EXPERTS = 2   /* routed gated experts (+ identity experts, + a shared expert) */
+    TI_SEQ_FF_EXPERTS = 2,  /* routed gated experts (+ identity experts, + a shared expert) */
+    TI_SEQ_FF_DENSE = 3     /* down(act(up h)) with ff_act (its learned numbers, if it has any, in "mlp.act") */
+};
+enum {
+    TI_SEQ_ROUTE_SOFTMAX_ALL = 0, /* softmax over all router outputs, choice by score + correction inside the best groups, weights renormalised */
+    TI_SEQ_ROUTE_TOP_LOGITS = 1   /* logits + bias ("mlp.router.b"); the `top` largest are chosen, weights = softmax over the chosen logits */
+};
+enum {
+    TI_SEQ_QK_NORM_NONE = 0,
+    TI_SEQ_QK_NORM_HEAD = 1,   /* q and k divided by their RMS per head (after rotation), no weights */
+    TI_SEQ_QK_NORM_WHOLE = 2   /* RMS over the whole projection (all heads at once) times a plain weight "mix.q.norm" / "mix.k.norm" */
+};
+enum {
+    TI_SEQ_NORMS_AROUND = 0, /* a norm in front of every sublayer ("norm1", "norm2") and one behind it ("norm1b", "norm2b") */
+    TI_SEQ_NORMS_BEHIND = 1  /* the sublayers read the residual stream itself; one norm behind each ("norm1", "norm2") */
 };
 enum { TI_SEQ_NORM_SCALAR = 0 /* one gain for all coordinates */, TI_SEQ_NORM_ONE_PLUS = 1 /* per-coordinate gain stored as w, applied as 1 + w */ };
 enum { TI_SEQ_BF16 = 0, TI_SEQ_F32 = 1 };   /* compute mode of a model, and element type of a tensor handed to set_tensor */
@@ -48,7 +65,7 @@ typedef struct ti_seq_layer_desc {
     float rot_base;
     int32_t rot_scaled;      /* 1: wavelength-dependent slow-down of the frequencies with the four numbers below */
     float rot_factor, rot_low, rot_high, rot_original;
-    int32_t qk_norm;         /* 1: q and k are divided by their RMS per head after rotation */
+    int32_t qk_norm;         /* TI_SEQ_QK_NORM_* */
     int32_t out_gate;        /* 1: head output times sigmoid of a per-head projection of the mixer input */
     float scale;             /* attention score scale */
     int32_t decay_rank;      /* wkv: inner size of the decay's two-matrix projection */
@@ -69,6 +86,18 @@ typedef struct ti_seq_layer_desc {
     int32_t shared_ff;       /* inner size of the expert every token uses, scaled by a sigmoid of one more projection; 0 = none */
     /* -- around the sublayers -- */
     int32_t res_gate;        /* 1: every sublayer's result is multiplied by sigmoid(R h + b) of its input before the norm behind it */
+    /* -- attention: what happens to a score between the dot product and the softmax, and which keys a row sees -- */
+    float softcap;           /* > 0: score <- cap * tanh(score / cap) after scaling */
+    int32_t talk;            /* 1: the heads' scores of a (query, key) pair are mixed before masking, score_h <- sum_g T[h][g] score_g, T = "mix.talk" [heads][heads] */
+    int32_t keep_first;      /* with a window: keys at positions < keep_first stay visible to every later row */
+    /* (`sink` above also applies to TI_SEQ_MIXER_ATTENTION: "mix.sink" [heads]) */
+    /* -- feed-forward, routed experts -- */
+    int32_t route_kind;      /* TI_SEQ_ROUTE_* */
+    int32_t shared_plain;    /* 1: the shared expert is added as it is (no sigmoid scale, no "mlp.shared.sg") */
+    /* -- around the sublayers -- */
+    int32_t conv_taps;       /* > 1: the mixer reads h + conv(h), a causal depth-wise convolution over the last `conv_taps` inputs of the
+                                sequence ("canon1" [width][taps], zeros before position 0); the last taps - 1 inputs are sequence state */
+    int32_t layer_scale;     /* 1: each sublayer's normed result is multiplied coordinate by coordinate by "ls1" / "ls2" before the residual sum */
 } ti_seq_layer_desc;
 
 typedef struct ti_seq_model_desc {
@@ -84,6 +113,10 @@ typedef struct ti_seq_model_desc {
     float logit_softcap;     /* > 0: logits <- cap * tanh(logits / cap) */
     int32_t side_dim;        /* > 0: after every layer a per-token side input is added: side.embed[token][layer * side_dim ...] gated by
                                 gelu_tanh(side.gate x), projected back and RMS-normed with a plain per-coordinate weight */
+    int32_t norm_place;      /* TI_SEQ_NORMS_* */
+    float pos_base;          /* > 0: a sinusoidal position vector is added to the embedding: entry 2i = sin(p * base^(-2i/width)),
+                                entry 2i + 1 = cos of the same angle */
+    int32_t tied_head;       /* 1: the logits are products with the embedding table (no "head" tensor) */
 } ti_seq_model_desc;
 
 int ti_seq_init(int device);
@@ -92,7 +125,7 @@ uint64_t ti_seq_launch_count(void);
 
 int ti_seq_model_new(const ti_seq_model_desc* desc, const ti_seq_layer_desc* layers, ti_seq_model_t* out);
 /* tensor names: "embed", "side.embed", "loop.in", "final.norm", "head", "l<i>.norm1|norm1b|norm2|norm2b", "l<i>.rg1|rg2[.b]",
- * "l<i>.mix.<x>", "l<i>.mlp.<x>", "l<i>.side.<x>";
+ * "l<i>.ls1|ls2", "l<i>.canon1", "l<i>.mix.<x>", "l<i>.mlp.<x>", "l<i>.side.<x>";
  * `dtype` is the element type of `data` (TI_SEQ_BF16: raw bfloat16 bits, TI_SEQ_F32) */
 int ti_seq_model_set_tensor(ti_seq_model_t m, const char* name, int32_t dtype, const void* data, const int64_t* shape, int32_t ndim);
 /* uniform(-amp, amp) + offset generated on the device from (seed, element index): benchmark-size models */

@@ -22,6 +22,7 @@
 #include "seq_recurrent.cuh"
 #include "seq_latent.cuh"
 #include "seq_experts.cuh"
+#include "seq_headmix.cuh"
 #include "sampling.cuh"
 
 using namespace tib;
@@ -195,6 +196,11 @@ struct LayerW {
     // per-token side input
     const void *side_gate = nullptr, *side_proj = nullptr;
     const float* side_norm = nullptr;
+    // attention with a whole-projection q / k norm, mixed heads; the short convolution in front of the mixer; a dense feed-forward's
+    // activation numbers (xielu: softplus(act[0]), 1/2 + softplus(act[1])); the router's bias
+    const float *qnorm = nullptr, *knorm = nullptr, *talk = nullptr, *canon = nullptr, *route_bias = nullptr;
+    float act_a = 0.f, act_b = 0.f;
+    int mix_R = 0, mix_HP = 0;   // head-mixing attention: rows a block owns in prompt portions, register bound of the head count
 };
 
 // one execution of a layer: a looped layer runs several times, every run with its own cache or state
@@ -204,6 +210,7 @@ struct Run {
     DevBuf<float> k_pool, v_pool;          // attention: [pages * 64][G * d], [pages * 64][G * dv]; latent attention: k_pool [pages * 64][rank + rot]
     DevBuf<float> state, prev;             // wkv: [slots][H][d][d], [slots][D]; gla / hgrn2: state [slots][H][dk][dv]
     int kv_run = -1;                       // latent attention reading another layer's cache: the run that owns it
+    DevBuf<float> conv_state;              // short convolution: [slots][taps - 1][D], the last inputs of every sequence
 };
 
 struct SeqState {
@@ -222,6 +229,7 @@ struct Model {
     size_t wsize = 2;                 // bytes per matrix element
     const void *embed = nullptr, *loop_in = nullptr, *head = nullptr, *side_embed = nullptr;
     const float* final_norm = nullptr;
+    DevBuf<float> pos_freq;           // sinusoidal positions: [ceil(width / 2)] frequencies
     int gvec = 0;                     // 1: the norms around the sublayers have one gain per coordinate
     // cache manager
     int num_pages = 0;
@@ -229,7 +237,8 @@ struct Model {
     std::vector<SeqState> seqs;
     // step scratch
     int cap_rows = 0, cap_want = 0;
-    DevBuf<float> x, x0, xc, h, proj, mixes, att, mo, act, lora, hn, logits, logprobs;
+    DevBuf<float> x, x0, xc, h, hc, proj, mixes, att, mo, act, lora, hn, logits, logprobs;   // hc: the mixer input behind a short convolution
+    bool any_conv = false;
     DevBuf<float> aux, aux2, route, rgbuf;   // decays / absorbed queries, weighted latent sums, routing weights, unfused residual gates
     int max_aux = 0, max_aux2 = 0, max_route = 0;
     bool any_rgbuf = false;
@@ -282,8 +291,17 @@ int describe_tensors(Model& m) {
     for (int i = 0; i < m.d.n_layers; ++i) {
         const ti_seq_layer_desc& L = m.layers[i].d;
         const std::string p = "l" + std::to_string(i) + ".";
+        const bool behind = m.d.norm_place == TI_SEQ_NORMS_BEHIND;
         require(m, p + "norm1", gain_shape, false);
-        require(m, p + "norm1b", gain_shape, false);
+        if (!behind) require(m, p + "norm1b", gain_shape, false);
+        if (L.layer_scale) {
+            require(m, p + "ls1", {D}, false);
+            if (L.ff > 0) require(m, p + "ls2", {D}, false);
+        }
+        if (L.conv_taps > 1 && L.mixer != TI_SEQ_MIXER_ATTENTION) return fail("layer %d: the short convolution is built in front of attention mixers", i);
+        if (L.conv_taps > 1) require(m, p + "canon1", {D, (int64_t)L.conv_taps}, false);
+        else if (L.conv_taps < 0) return fail("layer %d: %d convolution taps", i, L.conv_taps);
+        if (behind && (L.res_gate || L.mixer != TI_SEQ_MIXER_ATTENTION)) return fail("layer %d: norms behind the sublayers only are built for attention layers without residual gates", i);
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             if (L.heads <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) return fail("layer %d: heads %d / kv_heads %d", i, L.heads, L.kv_heads);
             if (L.dim <= 0 || L.vdim <= 0 || L.dim > 32 * kAttnMaxPerLane || L.vdim > 32 * kAttnMaxPerLane)
@@ -294,6 +312,18 @@ int describe_tensors(Model& m) {
             require(m, p + "mix.v", {(int64_t)L.kv_heads * L.vdim, D}, true);
             if (L.out_gate) require(m, p + "mix.g", {(int64_t)L.heads, D}, true);
             require(m, p + "mix.o", {D, (int64_t)L.heads * L.vdim}, true);
+            if (L.qk_norm == TI_SEQ_QK_NORM_WHOLE) {
+                if (L.rot_dims > 0 || L.out_gate) return fail("layer %d: the whole-projection q / k norm is built without rotation and output gate", i);
+                require(m, p + "mix.q.norm", {(int64_t)L.heads * L.dim}, false);
+                require(m, p + "mix.k.norm", {(int64_t)L.kv_heads * L.dim}, false);
+            } else if (L.qk_norm != TI_SEQ_QK_NORM_NONE && L.qk_norm != TI_SEQ_QK_NORM_HEAD) return fail("layer %d: q / k norm kind %d", i, L.qk_norm);
+            if (L.talk) require(m, p + "mix.talk", {(int64_t)L.heads, (int64_t)L.heads}, false);
+            if (L.sink) require(m, p + "mix.sink", {(int64_t)L.heads}, false);
+            if (L.keep_first < 0 || L.softcap < 0.f) return fail("layer %d: keep_first %d softcap %g", i, L.keep_first, L.softcap);
+            if (L.talk || L.softcap > 0.f || L.keep_first > 0) {   // the head-mixing kernel takes the layer
+                if (L.out_gate || L.qk_norm == TI_SEQ_QK_NORM_HEAD || L.rot_dims > 0) return fail("layer %d: capped / mixed scores and kept first keys are built without rotation, per-head norm and output gate", i);
+                if (L.heads > 64) return fail("layer %d: %d heads exceed the 64 the head-mixing attention holds in registers", i, L.heads);
+            }
         } else if (L.mixer == TI_SEQ_MIXER_WKV) {
             if (L.heads <= 0 || L.dim <= 0 || L.dim > 1024 || L.decay_rank <= 0) return fail("layer %d: wkv heads %d dim %d rank %d", i, L.heads, L.dim, L.decay_rank);
             const int64_t C = (int64_t)L.heads * L.dim;
@@ -354,8 +384,15 @@ int describe_tensors(Model& m) {
         }
         if (L.ff > 0) {
             require(m, p + "norm2", gain_shape, false);
-            require(m, p + "norm2b", gain_shape, false);
-            if (L.ff_kind == TI_SEQ_FF_GLU) {
+            if (!behind) require(m, p + "norm2b", gain_shape, false);
+            if (behind && L.ff_kind != TI_SEQ_FF_DENSE && L.ff_kind != TI_SEQ_FF_EXPERTS) return fail("layer %d: norms behind the sublayers only are built for the dense and the routed feed-forward", i);
+            if (L.ff_kind == TI_SEQ_FF_DENSE) {
+                if (L.ff_act != TI_SEQ_ACT_XIELU && L.ff_act != TI_SEQ_ACT_RELU && L.ff_act != TI_SEQ_ACT_SILU && L.ff_act != TI_SEQ_ACT_GELU_TANH)
+                    return fail("layer %d: activation %d", i, L.ff_act);
+                require(m, p + "mlp.up", {(int64_t)L.ff, D}, true);
+                require(m, p + "mlp.down", {D, (int64_t)L.ff}, true);
+                if (L.ff_act == TI_SEQ_ACT_XIELU) require(m, p + "mlp.act", {2}, false);
+            } else if (L.ff_kind == TI_SEQ_FF_GLU) {
                 require(m, p + "mlp.gate", {(int64_t)L.ff, D}, true);
                 require(m, p + "mlp.up", {(int64_t)L.ff, D}, true);
                 require(m, p + "mlp.down", {D, (int64_t)L.ff}, true);
@@ -374,12 +411,17 @@ int describe_tensors(Model& m) {
                     require(m, q + "down", {D, (int64_t)L.ff}, true);
                 }
                 require(m, p + "mlp.router", {(int64_t)n, D}, true);
-                require(m, p + "mlp.correction", {(int64_t)n}, false);
+                if (L.route_kind == TI_SEQ_ROUTE_TOP_LOGITS) {
+                    if (L.groups != 1 || L.groups_keep != 1) return fail("layer %d: the choice by logits has no groups", i);
+                    require(m, p + "mlp.router.b", {(int64_t)n}, false);
+                } else if (L.route_kind == TI_SEQ_ROUTE_SOFTMAX_ALL) {
+                    require(m, p + "mlp.correction", {(int64_t)n}, false);
+                } else return fail("layer %d: router kind %d", i, L.route_kind);
                 if (L.shared_ff > 0) {
                     require(m, p + "mlp.shared.gate", {(int64_t)L.shared_ff, D}, true);
                     require(m, p + "mlp.shared.up", {(int64_t)L.shared_ff, D}, true);
                     require(m, p + "mlp.shared.down", {D, (int64_t)L.shared_ff}, true);
-                    require(m, p + "mlp.shared.sg", {1, D}, true);
+                    if (!L.shared_plain) require(m, p + "mlp.shared.sg", {1, D}, true);
                 }
             } else {
                 return fail("layer %d: unknown feed-forward kind %d", i, L.ff_kind);
@@ -396,7 +438,9 @@ int describe_tensors(Model& m) {
         }
     }
     require(m, "final.norm", gain_shape, false);
-    require(m, "head", {V, D}, true);
+    if (!m.d.tied_head) require(m, "head", {V, D}, true);
+    if (m.d.norm_place != TI_SEQ_NORMS_AROUND && m.d.norm_place != TI_SEQ_NORMS_BEHIND) return fail("norm placement %d", m.d.norm_place);
+    if (m.d.norm_place == TI_SEQ_NORMS_BEHIND && (m.d.loop_times > 0 || m.d.side_dim > 0)) return fail("norms behind the sublayers only are built without a looped block and side input");
     return 0;
 }
 
@@ -476,6 +520,9 @@ int concat_cols(Model& m, const std::vector<const Tensor*>& parts, DevBuf<uint8_
     *cols = (int)total;
     return 0;
 }
+__global__ void mul_vec_kernel(float* w, const float* v, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) w[i] *= v[i];
+}
 __global__ void add_one_kernel(float* w, size_t n) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) w[i] += 1.f;
 }
@@ -534,7 +581,7 @@ struct Fuse {
 bool few_rows(int M, int K) { return M <= kRowGemvMaxRows && (size_t)M * K * sizeof(float) <= g_smem_optin; }
 
 int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, int M, int N, int K, int epi = EPI_NONE, float alpha = 1.f,
-         const Fuse* fuse = nullptr) {
+         const Fuse* fuse = nullptr, float beta = 0.f) {
     if (M <= 0 || N <= 0) return 0;
     const size_t xs_bytes = (size_t)M * K * sizeof(float);
     // few rows of a very long K that do not fit shared memory together (the side-by-side down matrices of many experts): in halves,
@@ -546,8 +593,8 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
     const bool plain = !fuse || (!fuse->norm_gain && !fuse->glu_ff);   // (a request to skip unused experts' rows is only a permission)
     if (plain && M > 1 && M <= kRowGemvMaxRows && !mma_ok && !few_rows(M, K) && few_rows(1, K)) {
         const int half = M / 2;
-        TRY(gemm(m, A, lda, W, C, ldc, half, N, K, epi, alpha, fuse));
-        return gemm(m, A + (size_t)half * lda, lda, W, C + (size_t)half * ldc, ldc, M - half, N, K, epi, alpha, fuse);
+        TRY(gemm(m, A, lda, W, C, ldc, half, N, K, epi, alpha, fuse, beta));
+        return gemm(m, A + (size_t)half * lda, lda, W, C + (size_t)half * ldc, ldc, M - half, N, K, epi, alpha, fuse, beta);
     }
     if (mma_ok || few_rows(M, K)) {
         const int warps = kRowGemvThreads / 32;
@@ -570,10 +617,10 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
             cfg.attrs = attr;
             cfg.numAttrs = g_use_pdl ? 1 : 0;
             if (f.glu_ff > 0)
-                CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<true>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+                CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<true>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, beta, f.norm_gain, f.eps, f.glu_ff,
                                       f.glu_act, f.gvec, f.nskip, f.kskip));
             else
-                CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<false>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+                CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<false>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, beta, f.norm_gain, f.eps, f.glu_ff,
                                       f.glu_act, f.gvec, f.nskip, f.kskip));
             LAUNCHED();
             return 0;
@@ -589,10 +636,10 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         cfg.attrs = attr;
         cfg.numAttrs = g_use_pdl ? 1 : 0;
         if (m.d.mode == TI_SEQ_BF16)
-            CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<__nv_bfloat16>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps,
+            CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<__nv_bfloat16>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, beta, f.norm_gain, f.eps,
                                   f.glu_ff, f.glu_act, f.gvec));
         else
-            CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<float>, A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+            CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<float>, A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, beta, f.norm_gain, f.eps, f.glu_ff,
                                   f.glu_act, f.gvec));
         LAUNCHED();
         return 0;
@@ -607,14 +654,14 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         TRY(make_tmap_bf16(&ma, m.abf.p, (uint64_t)K, (uint64_t)M));
         TRY(make_tmap_bf16(&mw, W, (uint64_t)K, (uint64_t)N));
         TcArgs g{};
-        g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.epi = epi; g.alpha = alpha; g.err = m.err.p;
+        g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.epi = epi; g.alpha = alpha; g.beta = beta; g.err = m.err.p;
         gemm_bf16_tc_kernel<<<dim3((N + kSgBN - 1) / kSgBN, (M + kSgBM - 1) / kSgBM), kSgThreads, kSgSmemBytes, g_stream>>>(ma, mw, g);
         LAUNCHED();
         return 0;
     }
     dim3 grid((N + 63) / 64, (M + 63) / 64);
-    if (m.d.mode == TI_SEQ_BF16) gemm_bf16_kernel<<<grid, 128, 0, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha);
-    else gemm_f32_kernel<<<grid, 256, 0, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha);
+    if (m.d.mode == TI_SEQ_BF16) gemm_bf16_kernel<<<grid, 128, 0, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, beta);
+    else gemm_f32_kernel<<<grid, 256, 0, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, beta);
     LAUNCHED();
     return 0;
 }
@@ -643,6 +690,7 @@ int ensure_scratch(Model& m, int rows, int want) {
         TRY(m.x0.alloc(R * D));
         if (m.d.loop_times > 0) TRY(m.xc.alloc(R * 2 * D));
         TRY(m.h.alloc(R * D));
+        if (m.any_conv) TRY(m.hc.alloc(R * D));
         TRY(m.proj.alloc(R * (size_t)m.max_proj));
         if (m.any_wkv) TRY(m.mixes.alloc(5 * R * D));
         TRY(m.att.alloc(R * (size_t)m.max_att));
@@ -823,8 +871,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     CK(cudaEventRecord(m.ev0, g_stream));
     const bool bf = m.d.mode == TI_SEQ_BF16;
     const int nt = 256;
-    if (bf) TRY(launch_dep(embed_rows_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, (const __nv_bfloat16*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr));
-    else TRY(launch_dep(embed_rows_kernel<float>, dim3(T), dim3(nt), 0, (const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr));
+    if (bf) TRY(launch_dep(embed_rows_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, (const __nv_bfloat16*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr, (const float*)m.pos_freq.p));
+    else TRY(launch_dep(embed_rows_kernel<float>, dim3(T), dim3(nt), 0, (const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr, (const float*)m.pos_freq.p));
     LAUNCHED();
     const float eps = m.d.norm_eps;
     const int gv = m.gvec;
@@ -890,6 +938,31 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         }
         return 0;
     };
+    // attention whose scores are capped / mixed across the heads / see kept first keys: a block owns rows of one sequence and ALL heads
+    // (prompt portions in tiles of the layer's row count, the other rows one by one with their keys split over blocks, then merged)
+    auto mixed_attention = [&](const AttnShape& s, const LayerW& L, const float* q, const float* kp, const float* vp, float* out) -> int {
+        const auto launch = [&](int Rb, dim3 grid, const int* tl, int sub, const int* rl, int splits, float* part) -> int {
+            const size_t smem = (size_t)mix_layout(s.heads, s.kv_heads, s.dim, s.vdim, Rb, L.mix_HP, s.talk != nullptr).total * sizeof(float);
+            if (L.mix_HP == 8) TRY(launch_dep(heads_mixed_attention_kernel<8>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
+            else if (L.mix_HP == 16) TRY(launch_dep(heads_mixed_attention_kernel<16>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
+            else if (L.mix_HP == 32) TRY(launch_dep(heads_mixed_attention_kernel<32>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
+            else TRY(launch_dep(heads_mixed_attention_kernel<64>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
+            LAUNCHED();
+            return 0;
+        };
+        if (n_tiles > 0) {
+            const int sub = (kAttnTile + L.mix_R - 1) / L.mix_R;
+            TRY(launch(L.mix_R, dim3(n_tiles * sub), d_tiles, sub, nullptr, 1, nullptr));
+        }
+        if (n_small > 0) {
+            const int span = s.window > 0 ? std::min(s.window, max_pos + 1) + s.keep_first : max_pos + 1;
+            const int splits = std::max(1, std::min({(span + 31) / 32, kAttnMaxSplits, (2 * g_num_sms) / n_small}));
+            TRY(launch(1, dim3(n_small, splits), nullptr, 1, d_small, splits, m.attn_part.p));
+            TRY(launch_dep(attention_merge_kernel, dim3((n_small * s.heads + 7) / 8), dim3(256), 0, (const float*)m.attn_part.p, q, sm, s, d_small, n_small, splits, out));
+            LAUNCHED();
+        }
+        return 0;
+    };
     for (size_t ri = 0; ri < m.runs.size(); ++ri) {
         Run& R = m.runs[ri];
         LayerW& L = m.layers[R.layer];
@@ -901,16 +974,25 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const int mixer = L.d.mixer;
         const bool attn = mixer == TI_SEQ_MIXER_ATTENTION;
         // decode steps (few rows) fuse the norm in front of the attention projections into the product's prologue
-        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate;
+        const bool behind = m.d.norm_place == TI_SEQ_NORMS_BEHIND;   // the sublayers read the residual stream itself
+        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate && !behind && L.d.conv_taps <= 1;
         // the mixers with ONE fused input projection (residual gate included) take the norm into that product's prologue as well
         const bool fuse_front = few_rows(T, D) && (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2 || mixer == TI_SEQ_MIXER_LATENT) && !L.rg1;
         Fuse ff1;
         ff1.norm_gain = L.norm1; ff1.eps = eps; ff1.gvec = gv;
         const float* front_in = fuse_front ? m.x.p : m.h.p;
         const Fuse* front_fuse = fuse_front ? &ff1 : nullptr;
-        if (!(fuse_rows && attn) && !fuse_front) {
+        if (!(fuse_rows && attn) && !fuse_front && !behind) {
             TRY(launch_dep(rmsnorm_kernel, dim3(T), dim3(nt), 0, (const float*)m.x.p, (const int*)nullptr, D, L.norm1, gv, eps, m.h.p));
             LAUNCHED();
+        }
+        const float* mix_in = behind ? m.x.p : m.h.p;   // what the mixer reads
+        if (L.d.conv_taps > 1) {   // ... with the short convolution over the sequence's last inputs added; the slot then keeps the newest ones
+            TRY(launch_dep(short_conv_kernel, dim3(T), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, L.canon, (const float*)R.conv_state.p, m.hc.p));
+            LAUNCHED();
+            TRY(launch_dep(short_conv_save_kernel, dim3(E), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, R.conv_state.p));
+            LAUNCHED();
+            mix_in = m.hc.p;
         }
         const float* gate1 = nullptr;   // residual gate of the mixer: pre-activations and their row stride
         int gate1_ld = 0;
@@ -932,11 +1014,14 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 f.norm_gain = L.norm1; f.eps = eps; f.gvec = gv;
                 TRY(gemm(m, m.x.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D, EPI_NONE, 1.f, &f));
             } else {
-                TRY(gemm(m, m.h.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
+                TRY(gemm(m, mix_in, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
             }
-            TRY(launch_dep(attn_prepare_kernel, dim3(T), dim3(128), 0, m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p));
+            s.sink = L.sink; s.softcap = L.d.softcap; s.keep_first = L.d.keep_first; s.talk = L.talk;
+            if (L.d.qk_norm == TI_SEQ_QK_NORM_WHOLE) TRY(launch_dep(attn_prepare_whole_kernel, dim3(T), dim3(256), 0, m.proj.p, sm, s, L.qnorm, L.knorm, R.k_pool.p, R.v_pool.p));
+            else TRY(launch_dep(attn_prepare_kernel, dim3(T), dim3(128), 0, m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p));
             LAUNCHED();
-            TRY(attention(s, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
+            if (L.mix_R > 0) TRY(mixed_attention(s, L, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
+            else TRY(attention(s, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
             TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
         } else if (mixer == TI_SEQ_MIXER_WKV) {
             const int C = L.d.heads * L.d.dim, d = L.d.dim, rank = L.d.decay_rank;
@@ -1035,7 +1120,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         }
         if (L.d.ff > 0) {
             const bool fuse_ff = fuse_rows && L.d.ff_kind == TI_SEQ_FF_GLU;
-            TRY(post(L.norm1b, gv, fuse_ff ? nullptr : L.norm2, gate1, gate1_ld, L.rg1b, nullptr));
+            TRY(post(L.norm1b, gv, (fuse_ff || behind) ? nullptr : L.norm2, gate1, gate1_ld, L.rg1b, nullptr));
+            const float* ff_in = behind ? m.x.p : m.h.p;   // what the feed-forward reads
             const float* gate2 = nullptr;
             int gate2_ld = 0;
             if (L.d.res_gate && L.rg2) {
@@ -1049,7 +1135,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             const float* idw = nullptr;
             bool down_done = false;
             const int F = L.d.ff;
-            if (L.d.ff_kind == TI_SEQ_FF_GLU) {
+            if (L.d.ff_kind == TI_SEQ_FF_DENSE) {   // the activation rides in the up product's epilogue
+                const int epi = L.d.ff_act == TI_SEQ_ACT_XIELU ? EPI_XIELU : L.d.ff_act == TI_SEQ_ACT_SILU ? EPI_SILU : L.d.ff_act == TI_SEQ_ACT_GELU_TANH ? EPI_GELU_TANH : EPI_MAX0;
+                TRY(gemm(m, ff_in, D, L.ffront, m.act.p, F, T, F, D, epi, L.act_a, nullptr, L.act_b));
+            } else if (L.d.ff_kind == TI_SEQ_FF_GLU) {
                 if (fuse_ff) {   // norm -> [gate | up] -> act(gate) * up in one launch
                     Fuse f;
                     f.norm_gain = L.norm2; f.eps = eps; f.gvec = gv; f.glu_ff = F; f.glu_act = L.d.ff_act;
@@ -1067,6 +1156,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 const int nfw = L.n_ffront, Ex = L.d.experts;
                 RouteShape r{};
                 r.n_real = Ex; r.n_id = L.d.identity; r.top = L.d.top; r.groups = L.d.groups; r.keep = L.d.groups_keep;
+                r.by_logits = L.d.route_kind == TI_SEQ_ROUTE_TOP_LOGITS ? 1 : 0;
+                const float* route_vec = r.by_logits ? L.route_bias : L.correction;
                 float* wdense = m.route.p;
                 float* idw_buf = m.route.p + (size_t)T * std::max(Ex, 1);
                 const size_t rper = (size_t)(2 * (Ex + L.d.identity) + 2 * L.d.groups) * sizeof(float);
@@ -1074,16 +1165,16 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 const bool sparse = few_rows(T, D) && bf && Ex > 0 && L.off_up > 0 && T * rper <= 40 * 1024;
                 if (sparse) {
                     int* used = reinterpret_cast<int*>(idw_buf + T);
-                    TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, nfw, T, L.off_up, D));
-                    TRY(launch_dep(moe_route_kernel, dim3(1), dim3(T * 32), T * rper, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf, used));
+                    TRY(gemm(m, ff_in, D, L.ffront, m.proj.p, nfw, T, L.off_up, D));
+                    TRY(launch_dep(moe_route_kernel, dim3(1), dim3(T * 32), T * rper, (const float*)m.proj.p, nfw, L.off_router, r, route_vec, T, wdense, idw_buf, used));
                     LAUNCHED();
                     Fuse f;
                     f.nskip = ExpertSkip{used, 0, 2 * F, Ex};
-                    TRY(gemm(m, m.h.p, D, (const uint8_t*)L.ffront + (size_t)L.off_up * D * m.wsize, m.proj.p + L.off_up, nfw, T, nfw - L.off_up, D, EPI_NONE, 1.f, &f));
+                    TRY(gemm(m, ff_in, D, (const uint8_t*)L.ffront + (size_t)L.off_up * D * m.wsize, m.proj.p + L.off_up, nfw, T, nfw - L.off_up, D, EPI_NONE, 1.f, &f));
                 } else {
-                    TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, nfw, T, nfw, D));
+                    TRY(gemm(m, ff_in, D, L.ffront, m.proj.p, nfw, T, nfw, D));
                     const int rw = 4;
-                    TRY(launch_dep(moe_route_kernel, dim3((T + rw - 1) / rw), dim3(rw * 32), rw * rper, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf,
+                    TRY(launch_dep(moe_route_kernel, dim3((T + rw - 1) / rw), dim3(rw * 32), rw * rper, (const float*)m.proj.p, nfw, L.off_router, r, route_vec, T, wdense, idw_buf,
                                    (int*)nullptr));
                     LAUNCHED();
                 }
@@ -1233,6 +1324,10 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<320, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<320>()));
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<192, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<192>()));
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<160, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<160>()));
+    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     g_device = device;
@@ -1367,7 +1462,14 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
     auto P = [&](const std::string& nm) -> const void* { return T(nm)->data.p; };
     const int D = m.d.width;
     m.embed = P("embed");
-    m.head = P("head");
+    m.head = m.d.tied_head ? m.embed : P("head");
+    const bool behind = m.d.norm_place == TI_SEQ_NORMS_BEHIND;
+    if (m.d.pos_base > 0.f) {   // frequencies in double, rounded once
+        std::vector<float> f((size_t)(D + 1) / 2);
+        for (size_t i = 0; i < f.size(); ++i) f[i] = (float)std::pow((double)m.d.pos_base, -2.0 * (double)i / (double)D);
+        TRY(m.pos_freq.alloc(f.size()));
+        CK(cudaMemcpy(m.pos_freq.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+    }
     if (m.d.side_dim > 0) m.side_embed = P("side.embed");
     if (m.d.loop_times > 0) m.loop_in = P("loop.in");
     m.gvec = m.d.norm_kind == TI_SEQ_NORM_ONE_PLUS ? 1 : 0;
@@ -1382,6 +1484,20 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             }
         CK(cudaStreamSynchronize(g_stream));
     }
+    // layer scale: the gain of the norm behind a sublayer and the scale behind that norm are one multiplication per coordinate
+    for (int i = 0; i < m.d.n_layers; ++i) {
+        if (!m.layers[i].d.layer_scale) continue;
+        if (!m.gvec) return fail("finalize: layer scale needs norms with one gain per coordinate");
+        const std::string p = "l" + std::to_string(i) + ".";
+        for (int k = 1; k <= 2; ++k) {
+            Tensor* ls = T(p + "ls" + std::to_string(k));
+            Tensor* g = T(p + "norm" + std::to_string(k) + (behind ? "" : "b"));
+            if (!ls || !g) continue;
+            mul_vec_kernel<<<grid_for(g->count()), 256, 0, g_stream>>>(reinterpret_cast<float*>(g->data.p), reinterpret_cast<const float*>(ls->data.p), g->count());
+            LAUNCHED();
+        }
+        CK(cudaStreamSynchronize(g_stream));
+    }
     m.final_norm = F("final.norm");
     m.max_k = 2 * D;
     auto note_k = [&](int k) { m.max_k = std::max(m.max_k, k); };
@@ -1391,8 +1507,9 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
     for (int i = 0; i < m.d.n_layers; ++i) {
         LayerW& L = m.layers[i];
         const std::string p = "l" + std::to_string(i) + ".";
-        L.norm1 = F(p + "norm1");
-        L.norm1b = F(p + "norm1b");
+        if (behind) L.norm1b = F(p + "norm1");   // the only norm of the sublayer sits behind it
+        else { L.norm1 = F(p + "norm1"); L.norm1b = F(p + "norm1b"); }
+        if (L.d.conv_taps > 1) { L.canon = F(p + "canon1"); m.any_conv = true; }
         bool rg1_fused = false, rg2_fused = false;
         if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
             TRY(concat_rows(m, {T(p + "mix.q"), T(p + "mix.k"), T(p + "mix.v"), L.d.out_gate ? T(p + "mix.g") : nullptr}, L.qkvg_buf, &L.n_qkvg));
@@ -1405,6 +1522,19 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             m.max_proj = std::max(m.max_proj, L.n_qkvg);
             m.max_att = std::max(m.max_att, L.d.heads * L.d.vdim);
             m.max_heads_v = std::max(m.max_heads_v, L.d.heads * (L.d.vdim + 2));
+            if (L.d.qk_norm == TI_SEQ_QK_NORM_WHOLE) { L.qnorm = F(p + "mix.q.norm"); L.knorm = F(p + "mix.k.norm"); }
+            if (L.d.talk) L.talk = F(p + "mix.talk");
+            if (L.d.sink) L.sink = F(p + "mix.sink");
+            if (L.d.talk || L.d.softcap > 0.f || L.d.keep_first > 0) {
+                // rows a block owns in prompt portions: (heads x rows) score rows of 64 keys and as many output rows live in shared memory
+                const int H = L.d.heads;
+                L.mix_HP = H <= 8 ? 8 : H <= 16 ? 16 : H <= 32 ? 32 : 64;
+                int R = std::max(1, std::min(kAttnTile, 128 / H));
+                while (R > 1 && (size_t)mix_layout(H, L.d.kv_heads, L.d.dim, L.d.vdim, R, L.mix_HP, L.d.talk != 0).total * sizeof(float) > g_smem_optin) --R;
+                if ((size_t)mix_layout(H, L.d.kv_heads, L.d.dim, L.d.vdim, R, L.mix_HP, L.d.talk != 0).total * sizeof(float) > g_smem_optin)
+                    return fail("finalize: layer %d: %d heads of %d / %d do not fit the head-mixing attention's shared memory", i, H, L.d.dim, L.d.vdim);
+                L.mix_R = R;
+            }
         } else if (L.d.mixer == TI_SEQ_MIXER_WKV) {
             const int C = L.d.heads * L.d.dim;
             L.r = P(p + "mix.r"); L.k = P(p + "mix.k"); L.v = P(p + "mix.v"); L.g = P(p + "mix.g");
@@ -1480,9 +1610,23 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             if (!rg1_fused) { L.rg1 = P(p + "rg1"); m.any_rgbuf = true; }
         }
         if (L.d.ff > 0) {
-            L.norm2 = F(p + "norm2");
-            L.norm2b = F(p + "norm2b");
-            if (L.d.ff_kind == TI_SEQ_FF_GLU) {
+            if (behind) L.norm2b = F(p + "norm2");
+            else { L.norm2 = F(p + "norm2"); L.norm2b = F(p + "norm2b"); }
+            if (L.d.ff_kind == TI_SEQ_FF_DENSE) {
+                L.ffront = P(p + "mlp.up");
+                L.n_ffront = L.d.ff;
+                L.off_up = 0;
+                L.down = P(p + "mlp.down");
+                L.ff_width = L.d.ff;
+                if (L.d.ff_act == TI_SEQ_ACT_XIELU) {
+                    float a[2];
+                    CK(cudaMemcpy(a, F(p + "mlp.act"), sizeof(a), cudaMemcpyDeviceToHost));
+                    const auto softplus = [](double z) { return z > 30.0 ? z : std::log1p(std::exp(z)); };
+                    L.act_a = (float)softplus(a[0]);
+                    L.act_b = (float)(0.5 + softplus(a[1]));
+                }
+                m.max_proj = std::max(m.max_proj, L.d.ff);
+            } else if (L.d.ff_kind == TI_SEQ_FF_GLU) {
                 int rows = 0;
                 TRY(concat_rows(m, {T(p + "mlp.gate"), T(p + "mlp.up")}, L.gateup_buf, &rows));
                 L.gateup = L.gateup_buf.p;
@@ -1505,7 +1649,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
                 m.max_proj = std::max(m.max_proj, L.n_ffront);
             } else {
                 const int E = L.d.experts;
-                std::vector<const Tensor*> parts{T(p + "mlp.router"), L.d.shared_ff > 0 ? T(p + "mlp.shared.sg") : nullptr, L.d.res_gate ? T(p + "rg2") : nullptr};
+                std::vector<const Tensor*> parts{T(p + "mlp.router"), L.d.shared_ff > 0 && !L.d.shared_plain ? T(p + "mlp.shared.sg") : nullptr, L.d.res_gate ? T(p + "rg2") : nullptr};
                 std::vector<const Tensor*> downs;
                 for (int e = 0; e < E; ++e) {
                     const std::string q = p + "mlp.e" + std::to_string(e) + ".";
@@ -1534,7 +1678,8 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
                 for (int e = 0; e < E; ++e)
                     for (const char* s : {"gate", "up", "down"}) release(p + "mlp.e" + std::to_string(e) + "." + s);
                 for (const char* s : {"mlp.router", "mlp.shared.sg", "mlp.shared.gate", "mlp.shared.up", "mlp.shared.down", "rg2"}) release(p + s);
-                L.correction = F(p + "mlp.correction");
+                if (L.d.route_kind == TI_SEQ_ROUTE_TOP_LOGITS) L.route_bias = F(p + "mlp.router.b");
+                else L.correction = F(p + "mlp.correction");
                 m.max_proj = std::max(m.max_proj, L.n_ffront);
                 m.max_route = std::max(m.max_route, 2 * std::max(E, 1) + 1);   // weights, identity weight, and (few rows) the experts' used flags
             }
@@ -1578,6 +1723,10 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
         } else {
             TRY(R.state.alloc((size_t)m.d.max_seqs * L.heads * L.dim * L.vdim));
             CK(cudaMemset(R.state.p, 0, R.state.n * sizeof(float)));
+        }
+        if (L.conv_taps > 1) {
+            TRY(R.conv_state.alloc((size_t)m.d.max_seqs * (L.conv_taps - 1) * D));
+            CK(cudaMemset(R.conv_state.p, 0, R.conv_state.n * sizeof(float)));
         }
     }
     m.max_k = std::max({m.max_k, 2 * D, m.max_att, m.max_ff, m.max_rank, D});
@@ -1779,6 +1928,7 @@ int ti_seq_model_bytes(ti_seq_model_t h, double* weight_bytes, double* kv_bytes_
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             w += ((double)L.heads * L.dim + (double)L.kv_heads * (L.dim + L.vdim) + (L.out_gate ? L.heads : 0) + (double)L.heads * L.vdim) * D * ws;
             kv += (double)L.kv_heads * (L.dim + L.vdim) * 4;
+            if (L.conv_taps > 1) st += (double)(L.conv_taps - 1) * D * 4;
         } else if (L.mixer == TI_SEQ_MIXER_WKV) {
             const double C = (double)L.heads * L.dim;
             w += (5 * C * D + (double)L.decay_rank * (D + C)) * ws;
@@ -1800,12 +1950,12 @@ int ti_seq_model_bytes(ti_seq_model_t h, double* weight_bytes, double* kv_bytes_
         if (L.ff > 0) {
             // routed experts: the stacked products read every expert's weights whatever the tokens chose
             if (L.ff_kind == TI_SEQ_FF_GLU) w += 3.0 * L.ff * D * ws;
-            else if (L.ff_kind == TI_SEQ_FF_POLYNORM) w += 2.0 * L.ff * D * ws;
-            else w += (3.0 * ((double)L.experts * L.ff + L.shared_ff) + L.experts + L.identity + (L.shared_ff > 0 ? 1 : 0)) * D * ws;
+            else if (L.ff_kind == TI_SEQ_FF_POLYNORM || L.ff_kind == TI_SEQ_FF_DENSE) w += 2.0 * L.ff * D * ws;
+            else w += (3.0 * ((double)L.experts * L.ff + L.shared_ff) + L.experts + L.identity + (L.shared_ff > 0 && !L.shared_plain ? 1 : 0)) * D * ws;
         }
         if (m->d.side_dim > 0) w += 2.0 * m->d.side_dim * D * ws;
     }
-    w += (double)m->d.vocab * D * ws;
+    w += (double)m->d.vocab * D * ws;   // the head (the embedding table itself when the two are tied)
     if (weight_bytes) *weight_bytes = w;
     if (kv_bytes_per_token) *kv_bytes_per_token = kv;
     if (state_bytes_per_seq) *state_bytes_per_seq = st;

@@ -40,6 +40,8 @@ struct RouteShape {
     int n_real, n_id;    // experts with weights, identity experts behind them (router outputs = n_real + n_id)
     int top;             // experts a token uses
     int groups, keep;    // equal groups of neighbouring router outputs; only the `keep` groups with the largest member can be chosen
+    int by_logits;       // 1: `correction` is a bias added to the logits, the `top` largest biased logits are chosen and the weights are
+                         // the softmax over the chosen ones (no groups)
 };
 // One warp per row.  s = softmax(logits); choice = s + correction; the best `keep` groups by their largest choice score stay, the
 // `top` largest choice scores among them are picked (first index wins a tie); weights = s over the picked ones / (their sum + 1e-20).
@@ -59,18 +61,20 @@ __global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape 
     float* kept = gs + r.groups;
     const float* z = proj + (size_t)t * ld + off;
     float mx = -INFINITY;
-    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i]);
+    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i] + (r.by_logits ? correction[i] : 0.f));
     mx = warp_max(mx);
     float sum = 0.f;
     for (int i = lane; i < n; i += 32) {
-        const float e = expf(z[i] - mx);
+        const float e = expf(z[i] + (r.by_logits ? correction[i] : 0.f) - mx);
         s[i] = e;
         sum += e;
     }
     sum = warp_sum(sum);
     for (int i = lane; i < n; i += 32) {
-        s[i] = s[i] / sum;
-        ch[i] = s[i] + correction[i];
+        // by logits: the choice is made among the biased logits, and exp(. - max) of a chosen one over the chosen ones' sum is the
+        // softmax over the chosen logits (the largest logit is always among them, so nothing underflows that matters)
+        if (r.by_logits) { ch[i] = z[i] + correction[i]; s[i] = fmaxf(s[i], 1e-37f); }
+        else { s[i] = s[i] / sum; ch[i] = s[i] + correction[i]; }
     }
     __syncwarp();
     const int size = n / r.groups;
@@ -179,7 +183,8 @@ __global__ void moe_act_kernel(const float* proj, int ld, int off_gu, int E, int
         } else {
             const int c = x - E * F;
             const float g = row[off_sh + c], u = row[off_sh + Fs + c];
-            v = (g / (1.f + expf(-g))) * u / (1.f + expf(-row[off_sg]));
+            v = (g / (1.f + expf(-g))) * u;
+            if (off_sg >= 0) v /= 1.f + expf(-row[off_sg]);
         }
         act[i] = v;
     }

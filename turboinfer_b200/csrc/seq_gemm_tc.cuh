@@ -29,7 +29,7 @@ struct TcArgs {
     float* C;
     int ldc;
     int epi;
-    float alpha;
+    float alpha, beta;
     int* err;   // set to 1 when a wait ran out
 };
 
@@ -136,14 +136,14 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if ((g.ldc & 3) == 0 && nbase + 16 <= g.N && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0) {
 #pragma unroll
                     for (int i = 0; i < 16; i += 4) {
-                        float4 v = make_float4(epi_apply(__uint_as_float(a[i]), g.epi, g.alpha), epi_apply(__uint_as_float(a[i + 1]), g.epi, g.alpha),
-                                               epi_apply(__uint_as_float(a[i + 2]), g.epi, g.alpha), epi_apply(__uint_as_float(a[i + 3]), g.epi, g.alpha));
+                        float4 v = make_float4(epi_apply(__uint_as_float(a[i]), g.epi, g.alpha, g.beta), epi_apply(__uint_as_float(a[i + 1]), g.epi, g.alpha, g.beta),
+                                               epi_apply(__uint_as_float(a[i + 2]), g.epi, g.alpha, g.beta), epi_apply(__uint_as_float(a[i + 3]), g.epi, g.alpha, g.beta));
                         *reinterpret_cast<float4*>(crow + nbase + i) = v;
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        if (nbase + i < g.N) crow[nbase + i] = epi_apply(__uint_as_float(a[i]), g.epi, g.alpha);
+                        if (nbase + i < g.N) crow[nbase + i] = epi_apply(__uint_as_float(a[i]), g.epi, g.alpha, g.beta);
                 }
             }
         }

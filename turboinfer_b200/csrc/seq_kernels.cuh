@@ -51,15 +51,21 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ---- embedding -----------------------------------------------------------------------------------------------------
-// x[t] = embed[tok[t]]; x0 (optional) keeps the embedding output for the looped block's input projection
+// x[t] = embed[tok[t]] (+ the sinusoidal position vector: entry 2i = sin(pos * pos_freq[i]), entry 2i + 1 = cos of the same angle,
+// angle and functions in fp32); x0 (optional) keeps the embedding output for the looped block's input projection
 template <typename WT>
-__global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0) {
+__global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0, const float* pos_freq) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
     const WT* e = emb + (size_t)m.tok[t] * D;
+    const float pos = pos_freq ? (float)m.row_pos[t] : 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float v = to_f32(e[d]);
+        float v = to_f32(e[d]);
+        if (pos_freq) {
+            const float ang = pos * pos_freq[d >> 1];
+            v += (d & 1) ? cosf(ang) : sinf(ang);
+        }
         x[(size_t)t * D + d] = v;
         if (x0) x0[(size_t)t * D + d] = v;
     }
@@ -145,8 +151,16 @@ __global__ void postnorm_residual_kernel(PostArgs a) {
 }
 
 // ---- matrix products: C[M, N] = epi(A[M, K] . W[N, K]^T) ----------------------------------------------------------------
-enum { EPI_NONE = 0, EPI_TANH = 1, EPI_SCALE = 2, EPI_SILU = 3, EPI_SOFTCAP = 4 /* alpha * tanh(v / alpha) */, EPI_GELU_TANH = 5 };
-__device__ __forceinline__ float epi_apply(float v, int epi, float alpha) {
+enum {
+    EPI_NONE = 0, EPI_TANH = 1, EPI_SCALE = 2, EPI_SILU = 3, EPI_SOFTCAP = 4 /* alpha * tanh(v / alpha) */, EPI_GELU_TANH = 5,
+    EPI_XIELU = 6 /* alpha v^2 + v / 2 for v > 0, beta (exp(v) - 1 - v) + v / 2 otherwise */, EPI_MAX0 = 7
+};
+__device__ __forceinline__ float xielu(float v, float a_pos, float a_neg) {
+    return v > 0.f ? fmaf(a_pos * v, v, 0.5f * v) : fmaf(a_neg, expm1f(v) - v, 0.5f * v);
+}
+__device__ __forceinline__ float epi_apply(float v, int epi, float alpha, float beta = 0.f) {
+    if (epi == EPI_XIELU) return xielu(v, alpha, beta);
+    if (epi == EPI_MAX0) return fmaxf(v, 0.f);
     if (epi == EPI_TANH) return tanhf(v);
     if (epi == EPI_SCALE) return v * alpha;
     if (epi == EPI_SILU) return v / (1.f + expf(-v));
@@ -157,7 +171,7 @@ __device__ __forceinline__ float epi_apply(float v, int epi, float alpha) {
 
 // true fp32: 64 x 64 tile, 16-deep k-steps, 256 threads with 4 x 4 outputs each
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* A, int lda, const float* W, float* C, int ldc, int M, int N, int K,
-                                                        int epi, float alpha) {
+                                                        int epi, float alpha, float beta) {
     __shared__ float As[16][64 + 4], Ws[16][64 + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
@@ -189,7 +203,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* A, int lda, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
-            if (gm < M && gn < N) C[(size_t)gm * ldc + gn] = epi_apply(acc[i][j], epi, alpha);
+            if (gm < M && gn < N) C[(size_t)gm * ldc + gn] = epi_apply(acc[i][j], epi, alpha, beta);
         }
 }
 
@@ -201,7 +215,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 __global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N,
-                                                         int K, int epi, float alpha) {
+                                                         int K, int epi, float alpha, float beta) {
     constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;
     __shared__ __align__(16) __nv_bfloat16 As[BM * LD], Ws[BN * LD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
@@ -271,7 +285,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda,
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int gm = m0 + wm + i * 16 + g + (e >> 1) * 8, gn = n0 + wn + j * 8 + 2 * t4 + (e & 1);
-                if (gm < M && gn < N) C[(size_t)gm * ldc + gn] = epi_apply(acc[i][j][e], epi, alpha);
+                if (gm < M && gn < N) C[(size_t)gm * ldc + gn] = epi_apply(acc[i][j][e], epi, alpha, beta);
             }
 }
 
@@ -345,7 +359,7 @@ __device__ __forceinline__ void gemv_row_dot(const WT* w, const float* xs, int M
 // still running, and only then waits for that kernel's results (the rows).
 template <typename WT>
 __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
-                                                                  float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec) {
+                                                                  float alpha, float beta, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec) {
     extern __shared__ __align__(16) float xs[];   // [M][K]
     __shared__ float rss[kRowGemvMaxRows][kRowGemvThreads / 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -407,7 +421,7 @@ __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const flo
         if (lane == 0) {
 #pragma unroll
             for (int r = 0; r < kRowGemvMaxRows; ++r)
-                if (r < M) C[(size_t)r * ldc + n] = glu_ff > 0 ? ff_act(acc[r], glu_act) * acc2[r] : epi_apply(acc[r], epi, alpha);
+                if (r < M) C[(size_t)r * ldc + n] = glu_ff > 0 ? ff_act(acc[r], glu_act) * acc2[r] : epi_apply(acc[r], epi, alpha, beta);
         }
     }
 }
@@ -467,7 +481,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 template <bool GLU>
 __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N, int K, int epi,
-                                                           float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec, ExpertSkip nskip,
+                                                           float alpha, float beta, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec, ExpertSkip nskip,
                                                            ExpertSkip kskip) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int Kp = K + 32;
@@ -592,7 +606,7 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
                 v += red[(w * 2 + 0) * 128 + src];
                 if (GLU) v2 += red[(w * 2 + 1) * 128 + src];
             }
-            if (r < M && n0 + j < N) C[(size_t)r * ldc + n0 + j] = GLU ? ff_act(v, glu_act) * v2 : epi_apply(v, epi, alpha);
+            if (r < M && n0 + j < N) C[(size_t)r * ldc + n0 + j] = GLU ? ff_act(v, glu_act) * v2 : epi_apply(v, epi, alpha, beta);
         }
         __syncthreads();
     }
@@ -679,6 +693,10 @@ struct AttnShape {
     int v_ld;                         // token stride of the value pool; 0: kv_heads * vdim.  A cache whose values are the leading
                                       // coordinates of its key rows passes the key pool as the value pool and the key stride here.
     const float* sink;                // [heads] or null: the softmax denominator gains exp(sink[h]), a term without key or value
+    // read by the head-mixing kernel only (seq_headmix.cuh); the step sends a layer there when one of them is set
+    float softcap;                    // > 0: score <- cap * tanh(score / cap) after scaling
+    int keep_first;                   // with a window: keys at positions < keep_first stay visible
+    const float* talk;                // [heads][heads] or null: score_h <- sum_g talk[h][g] score_g before masking
 };
 __device__ __forceinline__ size_t attn_vstride(const AttnShape& s) { return s.v_ld ? (size_t)s.v_ld : (size_t)s.kv_heads * s.vdim; }
 // the end of a softmax with a sink: (max, sum) -> the factor for the accumulated weighted values

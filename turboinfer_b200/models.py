@@ -10,6 +10,11 @@ reads folder/config.json and folder/model.safetensors.  Registered architectures
                   key part shared by the heads, softmax sink, optional reuse of an earlier layer's cache), dense feed-forward with a
                   polynomial-norm activation or routed experts (group-limited choice, identity experts, shared expert), gated
                   residuals, a per-layer token side input and capped logits; runs on the layered sequence engine too.
+  * "Gulazen"  -- attention layers that read the residual stream itself through a short causal convolution, with one norm and a
+                  per-coordinate layer scale behind every sublayer: whole-projection query / key norm, capped scores mixed across
+                  the heads, a sliding window that keeps the first keys, a softmax sink; dense feed-forward with the xIELU
+                  activation or routed experts chosen by biased logits with a plain shared expert; sinusoidal positions added to
+                  the embedding, logits tied to the embedding table; runs on the layered sequence engine too.
   * "llama"    -- the quantized Llama-style decoder of the persistent decode kernel (turboinfer_b200.capi.Model); built from
                   {"hidden", "layers", "heads", "inter", "vocab"} and fp32 tensors under the reference's names.
 """
@@ -163,6 +168,64 @@ def _load_tudasun(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seq
     mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
     shapes = {k: tuple(getattr(v, "shape", ())) for k, v in weights.items()}
     desc, layers = tudasun_descs(cfg, mode, max_tokens, max_seqs, shapes)
+    return _seq.SeqModel(desc, layers).load(weights)
+
+
+def gulazen_descs(cfg: dict, mode: int, max_tokens: int, max_seqs: int, tensor_shapes: Dict[str, Tuple[int, ...]] = None):
+    """config.json of a Gulazen model -> (ModelDesc, [LayerDesc]).  Every size and constant comes from the configuration; the base
+    of the sinusoidal positions (10000) is fixed by the design."""
+    taps = int(_req(_req(cfg, "canon", "the model"), "taps", "canon"))
+    if taps < 1:
+        raise ValueError(f"config: canon.taps {taps}")
+    layers: List[_seq.LayerDesc] = []
+    for i, L in enumerate(_req(cfg, "layers", "the model")):
+        where = f"layer {i}"
+        kind = _req(L, "type", where)
+        if kind != "attention":
+            raise ValueError(f"{where}: unknown mixer type '{kind}'")
+        mx = _req(L, "mixer", where)
+        d = _seq.LayerDesc()
+        d.mixer = _seq.MIXER_ATTENTION
+        d.heads, d.kv_heads = int(_req(mx, "heads", where)), int(_req(mx, "kv_heads", where))
+        d.dim, d.vdim = int(_req(mx, "dim", where)), int(_req(mx, "vdim", where))
+        mask = _req(mx, "mask", where)
+        d.window, d.keep_first = int(_req(mask, "size", where + " mask")), int(_req(mask, "keep_first", where + " mask"))
+        if d.window < 1:
+            raise ValueError(f"{where}: mask.size {d.window}")
+        d.scale, d.softcap = float(_req(mx, "scale", where)), float(_req(mx, "softcap", where))
+        d.rot_dims, d.qk_norm, d.out_gate = 0, _seq.QK_NORM_WHOLE, 0
+        d.talk, d.sink = 1, 1
+        d.conv_taps, d.layer_scale = taps, 1
+        mlp = L.get("mlp")
+        if mlp:
+            fk = _req(mlp, "kind", where + " mlp")
+            if fk == "dense":
+                d.ff_kind, d.ff, d.ff_act = _seq.FF_DENSE, int(_req(mlp, "ff", where + " mlp")), _seq.ACT_XIELU
+            elif fk == "moe":
+                r = _req(mlp, "router", where + " mlp")
+                d.ff_kind, d.ff = _seq.FF_EXPERTS, int(_req(_req(mlp, "expert", where + " mlp"), "ff", where + " mlp.expert"))
+                d.experts, d.top = int(_req(r, "experts", where + " router")), int(_req(r, "top", where + " router"))
+                d.identity, d.groups, d.groups_keep = 0, 1, 1
+                d.route_kind, d.shared_plain = _seq.ROUTE_TOP_LOGITS, 1
+                sh = mlp.get("shared")
+                d.shared_ff = int(_req(sh, "ff", where + " mlp.shared")) if sh else 0
+            else:
+                raise ValueError(f"{where}: unknown feed-forward kind '{fk}'")
+        layers.append(d)
+    m = _seq.ModelDesc()
+    m.vocab, m.width, m.n_layers = int(_req(cfg, "vocab", "the model")), int(_req(cfg, "width", "the model")), len(layers)
+    m.norm_eps = float(_req(_req(cfg, "norm", "the model"), "eps", "norm"))
+    m.norm_kind, m.norm_place = _seq.NORM_ONE_PLUS, _seq.NORMS_BEHIND
+    m.logit_scale, m.logit_softcap = 1.0, 0.0
+    m.pos_base, m.tied_head = 10000.0, 1
+    m.mode, m.max_tokens, m.max_seqs = mode, int(max_tokens), int(max_seqs)
+    return m, layers
+
+
+@register("Gulazen")
+def _load_gulazen(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seqs: int):
+    mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
+    desc, layers = gulazen_descs(cfg, mode, max_tokens, max_seqs)
     return _seq.SeqModel(desc, layers).load(weights)
 
 

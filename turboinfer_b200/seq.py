@@ -12,9 +12,12 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 BF16, F32 = 0, 1
 MIXER_ATTENTION, MIXER_WKV, MIXER_GLA, MIXER_HGRN2, MIXER_LATENT = 0, 1, 2, 3, 4
-ACT_RELU, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
-FF_GLU, FF_POLYNORM, FF_EXPERTS = 0, 1, 2
+ACT_RELU, ACT_SILU, ACT_GELU_TANH, ACT_XIELU = 0, 1, 2, 3
+FF_GLU, FF_POLYNORM, FF_EXPERTS, FF_DENSE = 0, 1, 2, 3
 NORM_SCALAR, NORM_ONE_PLUS = 0, 1
+ROUTE_SOFTMAX_ALL, ROUTE_TOP_LOGITS = 0, 1
+QK_NORM_NONE, QK_NORM_HEAD, QK_NORM_WHOLE = 0, 1, 2
+NORMS_AROUND, NORMS_BEHIND = 0, 1
 
 
 class SeqError(RuntimeError):
@@ -28,7 +31,9 @@ class LayerDesc(C.Structure):
                 ("qk_norm", C.c_int32), ("out_gate", C.c_int32), ("scale", C.c_float), ("decay_rank", C.c_int32),
                 ("ff", C.c_int32), ("ff_act", C.c_int32), ("decay_tau", C.c_float), ("kv_rank", C.c_int32), ("kv_from", C.c_int32),
                 ("sink", C.c_int32), ("ff_kind", C.c_int32), ("experts", C.c_int32), ("identity", C.c_int32), ("top", C.c_int32),
-                ("groups", C.c_int32), ("groups_keep", C.c_int32), ("shared_ff", C.c_int32), ("res_gate", C.c_int32)]
+                ("groups", C.c_int32), ("groups_keep", C.c_int32), ("shared_ff", C.c_int32), ("res_gate", C.c_int32),
+                ("softcap", C.c_float), ("talk", C.c_int32), ("keep_first", C.c_int32), ("route_kind", C.c_int32),
+                ("shared_plain", C.c_int32), ("conv_taps", C.c_int32), ("layer_scale", C.c_int32)]
 
     def __init__(self, *a, **kw):
         super().__init__(*a, **kw)
@@ -40,7 +45,8 @@ class ModelDesc(C.Structure):
     _fields_ = [("vocab", C.c_int32), ("width", C.c_int32), ("n_layers", C.c_int32), ("loop_start", C.c_int32),
                 ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("norm_eps", C.c_float), ("logit_scale", C.c_float),
                 ("mode", C.c_int32), ("max_tokens", C.c_int32), ("max_seqs", C.c_int32), ("norm_kind", C.c_int32),
-                ("logit_softcap", C.c_float), ("side_dim", C.c_int32)]
+                ("logit_softcap", C.c_float), ("side_dim", C.c_int32), ("norm_place", C.c_int32), ("pos_base", C.c_float),
+                ("tied_head", C.c_int32)]
 
 
 _i32 = C.POINTER(C.c_int32)
