@@ -95,7 +95,7 @@ typedef struct ti_seq_layer_desc {
     int32_t route_kind;      /* TI_SEQ_ROUTE_* */
     int32_t shared_plain;    /* 1: the shared expert is added as it is (no sigmoid scale, no "mlp.shared.sg") */
     /* -- around the sublayers -- */
-    int32_t conv_taps;       /* > 1: the mixer reads h + conv(h), a causal depth-wise convolution over the last `conv_taps` inputs of the
+    int32_t conv_taps;       /* >= 1: the mixer reads h + conv(h), a causal depth-wise convolution over the last `conv_taps` inputs of the
                                 sequence ("canon1" [width][taps], zeros before position 0); the last taps - 1 inputs are sequence state */
     int32_t layer_scale;     /* 1: each sublayer's normed result is multiplied coordinate by coordinate by "ls1" / "ls2" before the residual sum */
 } ti_seq_layer_desc;

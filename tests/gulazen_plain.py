@@ -70,17 +70,17 @@ def visible(i, j, window, keep_first):
 def attention_scores(q, keys, mx):
     """q [H, d]; keys [n, G, d] -> capped scores [H, n] before the heads are mixed."""
     H, G = mx["heads"], mx["kv_heads"]
+    K = np.array(keys)                                       # [n, G, d]
     s = np.zeros((H, len(keys)))
     for h in range(H):
-        g = h // (H // G)
-        for j, kj in enumerate(keys):
-            s[h, j] = float(q[h] @ kj[g]) * mx["scale"]
+        s[h] = (K[:, h // (H // G)] @ q[h]) * mx["scale"]   # query head h reads key/value head floor(h / (H / G))
     cap = mx["softcap"]
     return cap * np.tanh(s / cap)
 
 
-def attention_token(W, p, mx, eps, h, pos, cache):
-    """One token of the attention mixer; cache = {"k": [...], "v": [...]} grows by this token."""
+def attention_token(W, p, mx, eps, h, pos, cache, sees=visible):
+    """One token of the attention mixer; cache = {"k": [...], "v": [...]} grows by this token.  `sees` can be replaced by a test
+    that wants to know what a wrong mask would give."""
     H, G, d, dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
     q = rms_div(W[p + "q"] @ h, eps) * W[p + "q.norm"]
     k = rms_div(W[p + "k"] @ h, eps) * W[p + "k.norm"]
@@ -90,7 +90,7 @@ def attention_token(W, p, mx, eps, h, pos, cache):
     s = attention_scores(q.reshape(H, d), cache["k"], mx)
     s = W[p + "talk"] @ s                                   # s'[h, j] = sum_g T[h, g] s[g, j]
     win, keep = mx["mask"]["size"], mx["mask"]["keep_first"]
-    seen = [j for j in range(pos + 1) if visible(pos, j, win, keep)]
+    seen = [j for j in range(pos + 1) if sees(pos, j, win, keep)]
     out = np.zeros((H, dv))
     for hh in range(H):
         g = hh // (H // G)
@@ -134,8 +134,9 @@ def expert_ff(W, p, mlp, h):
 class Sequence:
     """Token-by-token evaluation of one sequence."""
 
-    def __init__(self, cfg, weights):
+    def __init__(self, cfg, weights, sees=visible):
         self.cfg = cfg
+        self.sees = sees
         self.W = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
         self.pos = 0
         self.kv = [{"k": [], "v": []} for _ in cfg["layers"]]
@@ -151,11 +152,10 @@ class Sequence:
         for i, L in enumerate(cfg["layers"]):
             p = f"l{i}."
             h = short_conv(self.hist[i], x, W[p + "canon1"])
-            if self.hist[i]:
-                self.hist[i] = self.hist[i][1:] + [x.copy()]
+            self.hist[i] = (self.hist[i] + [x.copy()])[1:]
             if L["type"] != "attention":
                 raise ValueError(L["type"])
-            y = attention_token(W, p + "mix.", L["mixer"], eps, h, self.pos, self.kv[i])
+            y = attention_token(W, p + "mix.", L["mixer"], eps, h, self.pos, self.kv[i], self.sees)
             x = x + W[p + "ls1"] * norm_one_plus(y, W[p + "norm1"], eps)
             mlp = L.get("mlp")
             if mlp:
@@ -167,9 +167,9 @@ class Sequence:
         return W["embed"] @ norm_one_plus(x, W["final.norm"], eps)
 
 
-def run(cfg, weights, tokens):
+def run(cfg, weights, tokens, sees=visible):
     """logits [len(tokens), vocab] and the residual stream after every layer [layers, tokens, width]."""
-    s = Sequence(cfg, weights)
+    s = Sequence(cfg, weights, sees)
     logits = np.stack([s.feed(int(t)) for t in tokens])
     layers = np.transpose(np.array(s.layers_out), (1, 0, 2))
     return logits, layers

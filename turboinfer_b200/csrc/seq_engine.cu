@@ -298,8 +298,8 @@ int describe_tensors(Model& m) {
             require(m, p + "ls1", {D}, false);
             if (L.ff > 0) require(m, p + "ls2", {D}, false);
         }
-        if (L.conv_taps > 1 && L.mixer != TI_SEQ_MIXER_ATTENTION) return fail("layer %d: the short convolution is built in front of attention mixers", i);
-        if (L.conv_taps > 1) require(m, p + "canon1", {D, (int64_t)L.conv_taps}, false);
+        if (L.conv_taps >= 1 && L.mixer != TI_SEQ_MIXER_ATTENTION) return fail("layer %d: the short convolution is built in front of attention mixers", i);
+        if (L.conv_taps >= 1) require(m, p + "canon1", {D, (int64_t)L.conv_taps}, false);
         else if (L.conv_taps < 0) return fail("layer %d: %d convolution taps", i, L.conv_taps);
         if (behind && (L.res_gate || L.mixer != TI_SEQ_MIXER_ATTENTION)) return fail("layer %d: norms behind the sublayers only are built for attention layers without residual gates", i);
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
@@ -975,7 +975,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const bool attn = mixer == TI_SEQ_MIXER_ATTENTION;
         // decode steps (few rows) fuse the norm in front of the attention projections into the product's prologue
         const bool behind = m.d.norm_place == TI_SEQ_NORMS_BEHIND;   // the sublayers read the residual stream itself
-        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate && !behind && L.d.conv_taps <= 1;
+        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate && !behind && L.d.conv_taps < 1;
         // the mixers with ONE fused input projection (residual gate included) take the norm into that product's prologue as well
         const bool fuse_front = few_rows(T, D) && (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2 || mixer == TI_SEQ_MIXER_LATENT) && !L.rg1;
         Fuse ff1;
@@ -987,11 +987,13 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             LAUNCHED();
         }
         const float* mix_in = behind ? m.x.p : m.h.p;   // what the mixer reads
-        if (L.d.conv_taps > 1) {   // ... with the short convolution over the sequence's last inputs added; the slot then keeps the newest ones
+        if (L.d.conv_taps >= 1) {   // ... with the short convolution over the sequence's last inputs added; the slot then keeps the newest ones
             TRY(launch_dep(short_conv_kernel, dim3(T), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, L.canon, (const float*)R.conv_state.p, m.hc.p));
             LAUNCHED();
-            TRY(launch_dep(short_conv_save_kernel, dim3(E), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, R.conv_state.p));
-            LAUNCHED();
+            if (L.d.conv_taps > 1) {
+                TRY(launch_dep(short_conv_save_kernel, dim3(E), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, R.conv_state.p));
+                LAUNCHED();
+            }
             mix_in = m.hc.p;
         }
         const float* gate1 = nullptr;   // residual gate of the mixer: pre-activations and their row stride
@@ -1509,7 +1511,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
         const std::string p = "l" + std::to_string(i) + ".";
         if (behind) L.norm1b = F(p + "norm1");   // the only norm of the sublayer sits behind it
         else { L.norm1 = F(p + "norm1"); L.norm1b = F(p + "norm1b"); }
-        if (L.d.conv_taps > 1) { L.canon = F(p + "canon1"); m.any_conv = true; }
+        if (L.d.conv_taps >= 1) { L.canon = F(p + "canon1"); m.any_conv = true; }
         bool rg1_fused = false, rg2_fused = false;
         if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
             TRY(concat_rows(m, {T(p + "mix.q"), T(p + "mix.k"), T(p + "mix.v"), L.d.out_gate ? T(p + "mix.g") : nullptr}, L.qkvg_buf, &L.n_qkvg));
