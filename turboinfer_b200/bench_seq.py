@@ -53,9 +53,31 @@ def tudasun_config_for(size: str) -> dict:
             "token_side": {"dim": 64}, "vocab": z["vocab"], "width": D}
 
 
+def gulazen_config_for(size: str) -> dict:
+    """Seven attention layers behind a four-tap convolution: the size's heads and window with 4 kept first keys, capped and mixed
+    scores; dense xIELU feed-forwards in layers 0, 2, 4, 6 and routed experts (8 of a quarter of the dense inner size, 2 chosen by
+    logits, a shared expert of half the dense size) in layers 1, 3, 5."""
+    z = SIZES[size]
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": z["window"], "keep_first": 4},
+             "scale": 1.0 / math.sqrt(z["dim"]), "softcap": 50.0}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "router": {"experts": 8, "top": 2}, "shared": {"ff": z["ff"] // 2}}
+    return {"architecture": "Gulazen", "canon": {"taps": 4}, "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(7)],
+            "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
+
+
+def binusun_attention_config_for(size: str) -> dict:
+    """The closest existing model to a Gulazen one: seven Binusun attention layers (same heads, window and feed-forward size, rotary,
+    per-head unit norm, output gate, gated relu feed-forward), no recurrent layers, no looped block."""
+    cfg = config_for(size)
+    return {"architecture": "Binusun", "layers": [cfg["layers"][1]] * 7, "norm": cfg["norm"], "logit_scale": 1.0, "vocab": cfg["vocab"], "width": cfg["width"]}
+
+
 def build_synthetic(cfg: dict, rank: int, dtype: str, max_tokens: int, max_seqs: int) -> seq.SeqModel:
     mode = {"bfloat16": seq.BF16, "float32": seq.F32}[dtype]
-    if cfg["architecture"] == "Tudasun":
+    if cfg["architecture"] == "Gulazen":
+        desc, layers = models.gulazen_descs(cfg, mode, max_tokens, max_seqs)
+    elif cfg["architecture"] == "Tudasun":
         shapes = {f"l{i}.mix.a1": (rank, cfg["width"]) for i, L in enumerate(cfg["layers"]) if L["type"] == "gla"}
         shapes.update({f"l{i}.rg1": (cfg["width"], cfg["width"]) for i in range(len(cfg["layers"]))})
         desc, layers = models.tudasun_descs(cfg, mode, max_tokens, max_seqs, shapes)
@@ -65,8 +87,14 @@ def build_synthetic(cfg: dict, rank: int, dtype: str, max_tokens: int, max_seqs:
     m = seq.SeqModel(desc, layers)
     for k, (name, shape) in enumerate(m.tensor_specs()):
         leaf = name.split(".")[-1]
-        if cfg["architecture"] == "Tudasun" and (leaf in ("norm1", "norm1b", "norm2", "norm2b", "b", "correction") or name == "final.norm"):
+        if cfg["architecture"] in ("Tudasun", "Gulazen") and (leaf in ("norm1", "norm1b", "norm2", "norm2b", "b", "correction") or name == "final.norm"):
             amp, off = 0.1, (1.0 if name.endswith("a2.b") else 0.0)   # gains stored around zero, biases, router corrections
+        elif leaf in ("ls1", "ls2"):
+            amp, off = 0.25, 0.5
+        elif leaf == "canon1":
+            amp, off = 0.2, 0.0
+        elif leaf == "talk":
+            amp, off = 0.5 / math.sqrt(shape[-1]), 1.0 / shape[-1]
         elif leaf == "lower":
             amp, off = 0.45, 0.45
         elif leaf in ("sink", "act"):
@@ -96,7 +124,7 @@ def prompt(n: int, vocab: int, offset: int = 0):
 
 
 def measure_seq(size: str, dtype: str, n_prompt: int, n_new: int, batch: int, steps: int, warmup: int, design: str = "Binusun") -> dict:
-    cfg = tudasun_config_for(size) if design == "Tudasun" else config_for(size)
+    cfg = {"Tudasun": tudasun_config_for, "Gulazen": gulazen_config_for, "BinusunAttention": binusun_attention_config_for}.get(design, config_for)(size)
     m = build_synthetic(cfg, SIZES[size]["rank"], dtype, max_tokens=(n_prompt + n_new + 64) * max(batch, 1) + 64, max_seqs=max(batch, 1))
     V = cfg["vocab"]
     launches0 = seq.launch_count()
@@ -168,6 +196,15 @@ def compare_tudasun(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_
     out = {"size": size, "shape": SIZES[size], "prompt_tokens": n_prompt, "decode_steps": n_new}
     for design in ("Tudasun", "Binusun"):
         key = design.lower() + "_bf16"
+        out[key] = measure_seq(size, "bfloat16", n_prompt, n_new, 1, steps, warmup, design)
+        out[key + "_batch4"] = {k: v for k, v in measure_seq(size, "bfloat16", 256, n_new, 4, 1, 1, design).items() if k.startswith("decode") or k == "batch"}
+    return out
+
+
+def compare_gulazen(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_new: int = 64) -> dict:
+    """Gulazen next to the closest model of the library, seven Binusun attention layers on the same engine (bf16 weights both)."""
+    out = {"size": size, "shape": SIZES[size], "prompt_tokens": n_prompt, "decode_steps": n_new}
+    for design, key in (("Gulazen", "gulazen_bf16"), ("BinusunAttention", "binusun_attention_bf16")):
         out[key] = measure_seq(size, "bfloat16", n_prompt, n_new, 1, steps, warmup, design)
         out[key + "_batch4"] = {k: v for k, v in measure_seq(size, "bfloat16", 256, n_new, 4, 1, 1, design).items() if k.startswith("decode") or k == "batch"}
     return out

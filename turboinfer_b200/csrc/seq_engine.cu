@@ -200,7 +200,7 @@ struct LayerW {
     // activation numbers (xielu: softplus(act[0]), 1/2 + softplus(act[1])); the router's bias
     const float *qnorm = nullptr, *knorm = nullptr, *talk = nullptr, *canon = nullptr, *route_bias = nullptr;
     float act_a = 0.f, act_b = 0.f;
-    int mix_R = 0, mix_HP = 0;   // head-mixing attention: rows a block owns in prompt portions, register bound of the head count
+    int mix_HP = 0;   // > 0: the layer's attention is the head-mixing one; register bound of its head count (8 / 16 / 32 / 64)
 };
 
 // one execution of a layer: a looped layer runs several times, every run with its own cache or state
@@ -245,6 +245,8 @@ struct Model {
     DevBuf<int> meta, picks;
     DevBuf<__nv_bfloat16> abf;   // bf16 copy of a product's activations for the tcgen05 path: [rows][max_k]
     DevBuf<float> attn_part;     // split-key attention partials: [rows][heads][splits][vdim + 2]
+    DevBuf<float> mix_S, mix_den; // head-mixing attention: scores / weights [rows of a batch][heads][keys], 1 / denominators [rows][heads]
+    bool any_mixed = false;
     int max_heads_v = 0;         // max over attention layers of heads * (vdim + 2)
     DevBuf<int> err;             // device flag: a bounded wait in a kernel ran out
     int max_k = 0;
@@ -811,8 +813,24 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         }
     }
     const int n_tiles = (int)tiles.size() / 2, n_tiles128 = (int)tiles128.size() / 2, n_small = (int)small_rows.size();
+    // the head-mixing attention cuts EVERY entry into tiles of up to 64 rows and wants the tile of every row
+    std::vector<int> mtiles, row_tile;
+    if (m.any_mixed) {
+        row_tile.resize(T);
+        int r0 = 0;
+        for (int e = 0; e < E; ++e) {
+            for (int o = 0; o < counts[e]; o += kAttnTile) {
+                const int nrow = std::min(kAttnTile, counts[e] - o);
+                for (int r = 0; r < nrow; ++r) row_tile[r0 + o + r] = (int)mtiles.size() / 2;
+                mtiles.push_back(r0 + o);
+                mtiles.push_back(nrow);
+            }
+            r0 += counts[e];
+        }
+    }
+    const int n_mtiles = (int)mtiles.size() / 2;
     const size_t n_meta = (size_t)3 * T + (size_t)(E + 1) + 2 * (size_t)E + (size_t)std::max(n_out, 1) + (size_t)m.seqs.size() * stride +
-                          (size_t)3 * T + 4;
+                          (size_t)3 * T + 4 + mtiles.size() + row_tile.size();
     if (n_meta > m.meta_host_cap) {
         if (m.meta_host) cudaFreeHost(m.meta_host);
         m.meta_host = nullptr;
@@ -850,6 +868,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     std::copy(small_rows.begin(), small_rows.end(), h_small);
     int* h_tiles128 = h_small + small_rows.size();
     std::copy(tiles128.begin(), tiles128.end(), h_tiles128);
+    int* h_mtiles = h_tiles128 + tiles128.size();
+    std::copy(mtiles.begin(), mtiles.end(), h_mtiles);
+    int* h_row_tile = h_mtiles + mtiles.size();
+    std::copy(row_tile.begin(), row_tile.end(), h_row_tile);
     // the previous step's copy out of this pinned buffer has completed: every step ends with a stream synchronisation
     CK(cudaMemcpyAsync(m.meta.p, hp, n_meta * sizeof(int), cudaMemcpyHostToDevice, g_stream));
     StepMeta sm{};
@@ -864,6 +886,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     const int* d_tiles = sm.page_table + m.seqs.size() * stride;
     const int* d_small = d_tiles + tiles.size();
     const int* d_tiles128 = d_small + small_rows.size();
+    const int* d_mtiles = d_tiles128 + tiles128.size();
+    const int* d_row_tile = d_mtiles + mtiles.size();
     sm.table_stride = stride;
     sm.T = T;
     sm.E = E;
@@ -938,28 +962,55 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         }
         return 0;
     };
-    // attention whose scores are capped / mixed across the heads / see kept first keys: a block owns rows of one sequence and ALL heads
-    // (prompt portions in tiles of the layer's row count, the other rows one by one with their keys split over blocks, then merged)
+    // attention whose scores are capped / mixed across the heads / see kept first keys: three passes over a score scratch, in batches
+    // of tiles whose scratch stays within L2 (every entry is cut into tiles; short ones take the row kernels of each pass)
     auto mixed_attention = [&](const AttnShape& s, const LayerW& L, const float* q, const float* kp, const float* vp, float* out) -> int {
-        const auto launch = [&](int Rb, dim3 grid, const int* tl, int sub, const int* rl, int splits, float* part) -> int {
-            const size_t smem = (size_t)mix_layout(s.heads, s.kv_heads, s.dim, s.vdim, Rb, L.mix_HP, s.talk != nullptr).total * sizeof(float);
-            if (L.mix_HP == 8) TRY(launch_dep(heads_mixed_attention_kernel<8>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
-            else if (L.mix_HP == 16) TRY(launch_dep(heads_mixed_attention_kernel<16>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
-            else if (L.mix_HP == 32) TRY(launch_dep(heads_mixed_attention_kernel<32>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
-            else TRY(launch_dep(heads_mixed_attention_kernel<64>, grid, dim3(256), smem, q, sm, s, tl, Rb, sub, rl, splits, kp, vp, out, part));
+        const int H = s.heads, HG = s.heads / s.kv_heads;
+        int max_total = 1;
+        for (int t = 0; t < n_mtiles; ++t) max_total = std::max(max_total, mix_band(h_pos[mtiles[2 * t]], mtiles[2 * t + 1], s.window, s.keep_first).total);
+        const int ldu = (max_total + 63) / 64 * 64;
+        const size_t per_row = (size_t)H * ldu;
+        const size_t budget_rows = std::max<size_t>(kAttnTile, ((size_t)16 << 20) / per_row);   // 64 MiB of scores
+        for (int t0 = 0; t0 < n_mtiles;) {
+            int t1 = t0, rows = 0;
+            bool big = false, small = false;
+            while (t1 < n_mtiles && (t1 == t0 || (size_t)(rows + mtiles[2 * t1 + 1]) <= budget_rows)) {
+                rows += mtiles[2 * t1 + 1];
+                (mtiles[2 * t1 + 1] >= kAttnTiledMinRows ? big : small) = true;
+                ++t1;
+            }
+            TRY(m.mix_S.ensure((size_t)rows * per_row));
+            TRY(m.mix_den.ensure((size_t)rows * H));
+            MixArgs a{};
+            a.tiles = d_mtiles; a.row_tile = d_row_tile; a.tile0 = t0; a.row_base = mtiles[2 * t0]; a.ldu = ldu; a.small = kAttnTiledMinRows;
+            a.S = m.mix_S.p; a.inv_den = m.mix_den.p;
+            const int nt_b = t1 - t0, d4 = (s.dim + 3) / 4 * 4, dv4 = (s.vdim + 3) / 4 * 4;
+            if (big) {
+                TRY(launch_dep(mix_scores_tiles_kernel, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 4) * sizeof(float), q, sm, s, a, kp));
+                LAUNCHED();
+            }
+            if (small) {
+                TRY(launch_dep(mix_scores_rows_kernel, dim3(ldu / 64, rows, s.kv_heads), dim3(256), (size_t)HG * s.dim * sizeof(float), q, sm, s, a, kp));
+                LAUNCHED();
+            }
+            const dim3 g2(big ? kAttnTile : kAttnTiledMinRows - 1, nt_b);
+            if (L.mix_HP == 8) TRY(launch_dep(mix_softmax_kernel<8>, g2, dim3(256), 0, sm, s, a));
+            else if (L.mix_HP == 16) TRY(launch_dep(mix_softmax_kernel<16>, g2, dim3(256), 0, sm, s, a));
+            else if (L.mix_HP == 32) TRY(launch_dep(mix_softmax_kernel<32>, g2, dim3(256), 0, sm, s, a));
+            else TRY(launch_dep(mix_softmax_kernel<64>, g2, dim3(256), 0, sm, s, a));
             LAUNCHED();
-            return 0;
-        };
-        if (n_tiles > 0) {
-            const int sub = (kAttnTile + L.mix_R - 1) / L.mix_R;
-            TRY(launch(L.mix_R, dim3(n_tiles * sub), d_tiles, sub, nullptr, 1, nullptr));
-        }
-        if (n_small > 0) {
-            const int span = s.window > 0 ? std::min(s.window, max_pos + 1) + s.keep_first : max_pos + 1;
-            const int splits = std::max(1, std::min({(span + 31) / 32, kAttnMaxSplits, (2 * g_num_sms) / n_small}));
-            TRY(launch(1, dim3(n_small, splits), nullptr, 1, d_small, splits, m.attn_part.p));
-            TRY(launch_dep(attention_merge_kernel, dim3((n_small * s.heads + 7) / 8), dim3(256), 0, (const float*)m.attn_part.p, q, sm, s, d_small, n_small, splits, out));
-            LAUNCHED();
+            if (big) {
+                const size_t smem = ((size_t)64 * 68 + (size_t)64 * dv4) * sizeof(float);
+                if (dv4 <= 64) TRY(launch_dep(mix_values_tiles_kernel<1>, dim3(nt_b, H), dim3(256), smem, sm, s, a, vp, out));
+                else if (dv4 <= 128) TRY(launch_dep(mix_values_tiles_kernel<2>, dim3(nt_b, H), dim3(256), smem, sm, s, a, vp, out));
+                else TRY(launch_dep(mix_values_tiles_kernel<4>, dim3(nt_b, H), dim3(256), smem, sm, s, a, vp, out));
+                LAUNCHED();
+            }
+            if (small) {
+                TRY(launch_dep(mix_values_rows_kernel<kAttnMaxPerLane>, dim3(rows, H), dim3(kMixRowWarps * 32), (size_t)kMixRowWarps * s.vdim * sizeof(float), sm, s, a, vp, out));
+                LAUNCHED();
+            }
+            t0 = t1;
         }
         return 0;
     };
@@ -1022,7 +1073,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             if (L.d.qk_norm == TI_SEQ_QK_NORM_WHOLE) TRY(launch_dep(attn_prepare_whole_kernel, dim3(T), dim3(256), 0, m.proj.p, sm, s, L.qnorm, L.knorm, R.k_pool.p, R.v_pool.p));
             else TRY(launch_dep(attn_prepare_kernel, dim3(T), dim3(128), 0, m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p));
             LAUNCHED();
-            if (L.mix_R > 0) TRY(mixed_attention(s, L, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
+            if (L.mix_HP > 0) TRY(mixed_attention(s, L, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
             else TRY(attention(s, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
             TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
         } else if (mixer == TI_SEQ_MIXER_WKV) {
@@ -1326,10 +1377,11 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<320, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<320>()));
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<192, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<192>()));
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<160, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<160>()));
-    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(heads_mixed_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_scores_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_scores_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_values_tiles_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_values_tiles_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_values_tiles_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     g_device = device;
@@ -1528,14 +1580,11 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             if (L.d.talk) L.talk = F(p + "mix.talk");
             if (L.d.sink) L.sink = F(p + "mix.sink");
             if (L.d.talk || L.d.softcap > 0.f || L.d.keep_first > 0) {
-                // rows a block owns in prompt portions: (heads x rows) score rows of 64 keys and as many output rows live in shared memory
-                const int H = L.d.heads;
+                const int H = L.d.heads, d4 = (L.d.dim + 3) / 4 * 4, dv4 = (L.d.vdim + 3) / 4 * 4;
                 L.mix_HP = H <= 8 ? 8 : H <= 16 ? 16 : H <= 32 ? 32 : 64;
-                int R = std::max(1, std::min(kAttnTile, 128 / H));
-                while (R > 1 && (size_t)mix_layout(H, L.d.kv_heads, L.d.dim, L.d.vdim, R, L.mix_HP, L.d.talk != 0).total * sizeof(float) > g_smem_optin) --R;
-                if ((size_t)mix_layout(H, L.d.kv_heads, L.d.dim, L.d.vdim, R, L.mix_HP, L.d.talk != 0).total * sizeof(float) > g_smem_optin)
-                    return fail("finalize: layer %d: %d heads of %d / %d do not fit the head-mixing attention's shared memory", i, H, L.d.dim, L.d.vdim);
-                L.mix_R = R;
+                if ((size_t)2 * 64 * (d4 + 4) * sizeof(float) > g_smem_optin || ((size_t)64 * 68 + (size_t)64 * dv4) * sizeof(float) > g_smem_optin)
+                    return fail("finalize: layer %d: head sizes %d / %d do not fit the head-mixing attention's shared memory", i, L.d.dim, L.d.vdim);
+                m.any_mixed = true;
             }
         } else if (L.d.mixer == TI_SEQ_MIXER_WKV) {
             const int C = L.d.heads * L.d.dim;

@@ -3,13 +3,13 @@
 //
 //   * whole-projection query / key norm: q (all heads at once) and k are divided by the RMS over the WHOLE projection and
 //     multiplied by a plain per-coordinate weight, then k and v are appended to the row's page (attn_prepare_whole_kernel);
-//   * capped, head-mixed, windowed attention with kept first keys and a sink (heads_mixed_attention_kernel):
+//   * capped, head-mixed, windowed attention with kept first keys and a sink (the mix_* kernels, three passes):
 //         s_h(i, j)  = cap * tanh(scale * q_h(i) . k_g(h)(j) / cap)                  (cap <= 0: no cap)
 //         s'_h(i, j) = sum_g T[h][g] s_g(i, j)                                       (T null: no mixing)
 //         row i sees key j  <=>  j <= i and (window <= 0 or i - j < window or j < keep_first)
 //         p_h(i, j)  = exp(s'_h(i, j)) / (sum over seen j' of exp(s'_h(i, j')) + exp(sink_h))   (sink null: no extra term)
-//     The mixing needs the scores of ALL heads of a (query, key) pair at once, so a block owns rows of one sequence and every
-//     head, unlike the per-head kernels of seq_kernels.cuh / seq_attn_tc.cuh;
+//     The mixing needs the scores of ALL heads of a (query, key) pair at once, unlike the per-head kernels of seq_kernels.cuh /
+//     seq_attn_tc.cuh, whose softmax runs along with the scores;
 //   * a causal depth-wise short convolution over time in front of a mixer, y_t = x_t + sum_j w[:, j] x_(t - taps + 1 + j), whose
 //     last taps - 1 inputs are sequence state (short_conv_kernel, short_conv_save_kernel).
 //
@@ -82,266 +82,371 @@ __global__ void attn_prepare_whole_kernel(float* qkv, StepMeta m, AttnShape s, c
 }
 
 // ---- capped, head-mixed attention ------------------------------------------------------------------------------------------------
-// A block owns up to R consecutive rows of ONE sequence and ALL query heads.  The keys its rows can see are the kept first ones
-// below the window and the window's range, walked as one list in tiles of 64 keys.  Per key tile:
-//   A  for every key/value head g: its key tile and the query vectors of its heads go to shared memory, scores (2 queries x 4 keys
-//      a thread), scale and cap -> S[head * R + row][key]
-//   B  one thread per (row, key) column: the H scores are mixed through T (registers), the mask is applied (-inf)
-//   C  one warp per S row: running maximum and sum, S <- exp(S - max), the factor for what was accumulated before
-//   D  for every key/value head g: its value tile to shared memory, O[head * R + row] <- O * factor + P V (O in shared memory,
-//      a tile's sum in registers)
-// Two forms of the grid.  Prompt portions: `tiles` lists (first row, rows <= 64) pairs; block b takes rows [sub_i * R, ...) of tile
-// b / sub, finishes the softmax (sink included) and writes out[t][h * dv ..].  Single rows: `rows` lists rows, blockIdx.y is one of
-// `splits` chunks of the row's key list; the block leaves (max, sum, unnormalised O) per head in `part`
-// [row index][head][split][dv + 2], which attention_merge_kernel combines.
-constexpr int kMixKT = 64;
-struct MixLayout {   // shared memory, in floats
-    int R, d4, dv4, ldq, ldkv, ldS, HP;
-    int off_T, off_Q, off_KV, off_S, off_O, off_stat, total;
+// The mixing needs the scores of ALL heads of a (query, key) pair before any head's softmax can start, so the attention runs as
+// three passes over a score scratch in global memory (sized to stay in L2):
+//   1  scores: S[row][head][u] = cap * tanh(scale * q . k / cap) for every key u of the row's band -- register-tiled fp32 products of
+//      64 rows x 64 keys per block for prompt portions (mix_scores_tiles_kernel), one warp per key for single rows
+//      (mix_scores_rows_kernel);
+//   2  one block per row: the H scores of every key are mixed through T, the mask is applied, and every head's softmax (with the
+//      sink in the denominator) turns its scores into weights in place (mix_softmax_kernel);
+//   3  weighted values: out[row][head] = sum_u P[row][head][u] v(u) -- again 64 x 64 tiles for prompt portions
+//      (mix_values_tiles_kernel) and a split of the keys over the warps of a block for single rows (mix_values_rows_kernel).
+// Every entry of the step is cut into tiles of up to 64 rows of one sequence (`tiles`: first row, row count); tiles with fewer than
+// `small` rows go through the row kernels.  The keys a tile can see form its BAND, one list for all its rows: the kept first keys
+// that lie below the window of the tile's first row, then the range from that window's start to the tile's last row; u indexes
+// this list, and the mask of pass 2 removes what a single row must not see.
+struct MixBand {
+    int lo, nA, total;
+    __device__ __forceinline__ int key(int u) const { return u < nA ? u : lo + (u - nA); }
 };
-__host__ __device__ inline MixLayout mix_layout(int H, int G, int d, int dv, int R, int HP, bool talk) {
-    MixLayout L;
-    L.R = R; L.HP = HP;
-    L.d4 = (d + 3) / 4 * 4; L.dv4 = (dv + 3) / 4 * 4;
-    L.ldq = L.d4 + 4; L.ldkv = (L.d4 > L.dv4 ? L.d4 : L.dv4) + 4; L.ldS = kMixKT + 4;
-    int o = 0;
-    L.off_T = o; o += talk ? H * HP : 0;
-    L.off_Q = o; o += (H / G) * R * L.ldq;
-    L.off_KV = o; o += kMixKT * L.ldkv;
-    L.off_S = o; o += H * R * L.ldS;
-    L.off_O = o; o += H * R * L.dv4;
-    L.off_stat = o; o += 3 * H * R;
-    L.total = o;
-    return L;
+__host__ __device__ inline MixBand mix_band(int p0, int n, int window, int keep_first) {
+    MixBand b;
+    b.lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    b.nA = window > 0 ? (keep_first < b.lo ? keep_first : b.lo) : 0;
+    b.total = b.nA + (p0 + n - 1 - b.lo + 1);
+    return b;
 }
-__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
-    return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, fmaf(a.w, b.w, acc))));
+struct MixArgs {
+    const int* tiles;      // [n tiles][2]
+    const int* row_tile;   // [T] the tile of every row of the step
+    int tile0, row_base;   // first tile and first row of the batch the scratch holds (scratch row = row - row_base)
+    int ldu;               // keys the scratch holds per (row, head)
+    int small;             // tiles with fewer rows take the row kernels
+    float* S;              // [rows][H][ldu] scores, then weights
+    float* inv_den;        // [rows][H] 1 / softmax denominator
+};
+__device__ __forceinline__ float mix_cap(float v, const AttnShape& s) {
+    v *= s.scale;
+    return s.softcap > 0.f ? s.softcap * tanhf(v / s.softcap) : v;
 }
-template <int HP>
-__global__ void __launch_bounds__(256) heads_mixed_attention_kernel(const float* qkv, StepMeta m, AttnShape s, const int* tiles, int R, int sub, const int* rows,
-                                                                    int splits, const float* k_pool, const float* v_pool, float* out, float* part) {
+__device__ __forceinline__ size_t mix_token(const int* table, int j) { return (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens; }
+
+// pass 1, prompt portions: grid (band tiles of 64 keys, tiles of the batch, heads)
+__global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv, StepMeta m, AttnShape s, MixArgs a, const float* k_pool) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     extern __shared__ __align__(16) float mixsm[];
-    const int H = s.heads, G = s.kv_heads, HG = H / G, d = s.dim, dv = s.vdim;
-    const MixLayout L = mix_layout(H, G, d, dv, R, HP, s.talk != nullptr);
-    float* Tm = mixsm + L.off_T;
-    float* Qg = mixsm + L.off_Q;
-    float* KV = mixsm + L.off_KV;
-    float* S = mixsm + L.off_S;
-    float* O = mixsm + L.off_O;
-    float* mrow = mixsm + L.off_stat;
-    float* lrow = mrow + H * R;
-    float* crow = lrow + H * R;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, tx = tid & 15, ty = tid >> 4;
-    int row0, n, z = 0;
-    if (rows) {
-        row0 = rows[blockIdx.x];
-        n = 1;
-        z = blockIdx.y;
-    } else {
-        const int tile = blockIdx.x / sub, si = blockIdx.x % sub;
-        row0 = tiles[2 * tile] + si * R;
-        n = min(R, tiles[2 * tile + 1] - si * R);
-        if (n <= 0) return;
-    }
-    const int p0 = m.row_pos[row0], hi = p0 + n - 1;
+    const int tile = a.tile0 + blockIdx.y, row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1];
+    if (n < a.small) return;
+    const int p0 = m.row_pos[row0];
+    const MixBand b = mix_band(p0, n, s.window, s.keep_first);
+    const int u0 = blockIdx.x * 64;
+    if (u0 >= b.total) return;
+    const int d = s.dim, d4 = (d + 3) / 4 * 4, ldq = d4 + 4, h = blockIdx.z, g = h / (s.heads / s.kv_heads);
+    float* Qs = mixsm;
+    float* Ks = Qs + 64 * ldq;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
-    const int lo = (s.window > 0 && p0 - s.window + 1 > 0) ? p0 - s.window + 1 : 0;
-    const int nA = s.window > 0 ? min(s.keep_first, lo) : 0;   // kept first keys below the window's range
-    const int total = nA + (hi - lo + 1);
-    int u_begin = 0, u_end = total;
-    if (rows && splits > 1) {
-        const int chunk = (total + splits - 1) / splits;
-        u_begin = min(total, z * chunk);
-        u_end = min(total, u_begin + chunk);
+    const size_t kstride = (size_t)s.kv_heads * d;
+    const bool vec = (d % 4 == 0) && (s.ld % 4 == 0);
+    for (int i = tid; i < 64 * (d4 / 4); i += 256) {
+        const int r = i / (d4 / 4), k4 = (i % (d4 / 4)) * 4;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f), k = q;
+        if (r < n) {
+            const float* src = qkv + (size_t)(row0 + r) * s.ld + (size_t)h * d + k4;
+            if (vec) q = *reinterpret_cast<const float4*>(src);
+            else { q.x = src[0]; if (k4 + 1 < d) q.y = src[1]; if (k4 + 2 < d) q.z = src[2]; if (k4 + 3 < d) q.w = src[3]; }
+        }
+        if (u0 + r < b.total) {
+            const float* src = k_pool + mix_token(table, b.key(u0 + r)) * kstride + (size_t)g * d + k4;
+            if (vec) k = *reinterpret_cast<const float4*>(src);
+            else { k.x = src[0]; if (k4 + 1 < d) k.y = src[1]; if (k4 + 2 < d) k.z = src[2]; if (k4 + 3 < d) k.w = src[3]; }
+        }
+        *reinterpret_cast<float4*>(&Qs[r * ldq + k4]) = q;
+        *reinterpret_cast<float4*>(&Ks[r * ldq + k4]) = k;
     }
+    __syncthreads();
+    float sc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+    for (int k = 0; k < d4; k += 4) {
+        float4 qa[4], kk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qa[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ldq + k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kk[j] = *reinterpret_cast<const float4*>(&Ks[(tx + 16 * j) * ldq + k]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                sc[i][j] = fmaf(qa[i].x, kk[j].x, fmaf(qa[i].y, kk[j].y, fmaf(qa[i].z, kk[j].z, fmaf(qa[i].w, kk[j].w, sc[i][j]))));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+        if (r >= n) continue;
+        float* dst = a.S + ((size_t)(row0 + r - a.row_base) * s.heads + h) * a.ldu + u0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (u0 + tx + 16 * j < b.total) dst[tx + 16 * j] = mix_cap(sc[i][j], s);
+    }
+}
+
+// pass 1, single rows: grid (chunks of 64 keys, rows of the batch, key/value heads); a warp takes 8 keys, a lane the coordinates
+// lane, lane + 32, ...; the row's query heads of the group wait in shared memory
+__global__ void __launch_bounds__(256) mix_scores_rows_kernel(const float* qkv, StepMeta m, AttnShape s, MixArgs a, const float* k_pool) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    extern __shared__ __align__(16) float mixsm[];   // [H / G][d]
+    const int row = a.row_base + blockIdx.y, tile = a.row_tile[row], row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1];
+    if (n >= a.small) return;
+    const MixBand b = mix_band(m.row_pos[row0], n, s.window, s.keep_first);
+    const int u0 = blockIdx.x * 64;
+    if (u0 >= b.total) return;
+    const int d = s.dim, HG = s.heads / s.kv_heads, g = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < HG * d; i += 256) mixsm[i] = qkv[(size_t)row * s.ld + (size_t)g * HG * d + i];
+    __syncthreads();
+    const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
+    const size_t kstride = (size_t)s.kv_heads * d;
+    for (int c = 0; c < 8; ++c) {
+        const int u = u0 + warp * 8 + c;
+        if (u >= b.total) break;
+        const float* kr = k_pool + mix_token(table, b.key(u)) * kstride + (size_t)g * d;
+        for (int hl0 = 0; hl0 < HG; hl0 += 4) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int k = lane; k < d; k += 32) {
+                const float kv = kr[k];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (hl0 + q < HG) acc[q] = fmaf(mixsm[(hl0 + q) * d + k], kv, acc[q]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float v = warp_sum(acc[q]);
+                if (lane == 0 && hl0 + q < HG) a.S[((size_t)(row - a.row_base) * s.heads + g * HG + hl0 + q) * a.ldu + u] = mix_cap(v, s);
+            }
+        }
+    }
+}
+
+// pass 2: grid (64, tiles of the batch); block (r, tile) owns row r of the tile and all heads: every key's H scores are mixed in
+// registers and masked, then every head's weights exp(s - max) replace its scores and 1 / (their sum + exp(sink - max)) is kept
+template <int HP>
+__global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape s, MixArgs a) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    __shared__ __align__(16) float Tm[HP * HP];
+    __shared__ float red[8][HP];
+    __shared__ float top[HP];
+    const int tile = a.tile0 + blockIdx.y, row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1], r = blockIdx.x;
+    if (r >= n) return;
+    const int H = s.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int p0 = m.row_pos[row0], pos = p0 + r;
+    const MixBand b = mix_band(p0, n, s.window, s.keep_first);
     if (s.talk)
-        for (int i = tid; i < H * HP; i += 256) Tm[i] = (i % HP) < H ? s.talk[(i / HP) * H + i % HP] : 0.f;
-    for (int i = tid; i < H * R; i += 256) { mrow[i] = -INFINITY; lrow[i] = 0.f; }
-    for (int i = tid; i < H * R * L.dv4; i += 256) O[i] = 0.f;
-    const size_t kstride = (size_t)G * d, vstride = (size_t)G * dv;
-    const bool vecq = (d % 4 == 0) && (s.ld % 4 == 0), veck = d % 4 == 0, vecv = dv % 4 == 0;
-    const float inv_cap = s.softcap > 0.f ? 1.f / s.softcap : 0.f;
-    const int QV = HG * R;
-    for (int u0 = u_begin; u0 < u_end; u0 += kMixKT) {
-        const int kc = min(kMixKT, u_end - u0);
-        // ---- A: scores of every head ----
-        for (int g = 0; g < G; ++g) {
-            __syncthreads();
-            for (int i = tid; i < kMixKT * (L.d4 / 4); i += 256) {
-                const int c = i / (L.d4 / 4), k4 = (i % (L.d4 / 4)) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (c < kc) {
-                    const int u = u0 + c, j = u < nA ? u : lo + (u - nA);
-                    const float* src = k_pool + ((size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens) * kstride + (size_t)g * d + k4;
-                    if (veck) v = *reinterpret_cast<const float4*>(src);
-                    else {
-                        v.x = src[0];
-                        if (k4 + 1 < d) v.y = src[1];
-                        if (k4 + 2 < d) v.z = src[2];
-                        if (k4 + 3 < d) v.w = src[3];
-                    }
+        for (int i = tid; i < HP * HP; i += 256) Tm[i] = (i / HP < H && i % HP < H) ? s.talk[(i / HP) * H + i % HP] : 0.f;
+    __syncthreads();
+    float* base = a.S + (size_t)(row0 + r - a.row_base) * H * a.ldu;
+    float mx[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) mx[h] = -INFINITY;
+    for (int u = tid; u < b.total; u += 256) {
+        const int j = b.key(u);
+        const bool seen = j <= pos && (s.window <= 0 || pos - j < s.window || j < s.keep_first);
+        float sv[HP];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) sv[h] = h < H ? base[(size_t)h * a.ldu + u] : 0.f;
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+            if (h >= H) break;
+            float v = sv[h];
+            if (s.talk) {
+                v = 0.f;
+#pragma unroll
+                for (int g = 0; g < HP; g += 4) {
+                    const float4 tv = *reinterpret_cast<const float4*>(&Tm[h * HP + g]);
+                    v = fmaf(tv.x, sv[g], fmaf(tv.y, sv[g + 1], fmaf(tv.z, sv[g + 2], fmaf(tv.w, sv[g + 3], v))));
                 }
-                *reinterpret_cast<float4*>(&KV[c * L.ldkv + k4]) = v;
             }
-            for (int i = tid; i < QV * (L.d4 / 4); i += 256) {
-                const int qv = i / (L.d4 / 4), k4 = (i % (L.d4 / 4)) * 4, hl = qv / R, r = qv % R;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r < n) {
-                    const float* src = qkv + (size_t)(row0 + r) * s.ld + (size_t)(g * HG + hl) * d + k4;
-                    if (vecq) v = *reinterpret_cast<const float4*>(src);
-                    else {
-                        v.x = src[0];
-                        if (k4 + 1 < d) v.y = src[1];
-                        if (k4 + 2 < d) v.z = src[2];
-                        if (k4 + 3 < d) v.w = src[3];
-                    }
+            v = seen ? v : -INFINITY;
+            base[(size_t)h * a.ldu + u] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+        const float v = warp_max(mx[h]);
+        if (lane == 0) red[warp][h] = v;
+    }
+    __syncthreads();
+    if (tid < HP) {
+        float v = red[0][tid];
+        for (int w = 1; w < 8; ++w) v = fmaxf(v, red[w][tid]);
+        if (s.sink && tid < H) v = fmaxf(v, s.sink[tid]);
+        top[tid] = v;
+    }
+    __syncthreads();
+    float sum[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) sum[h] = 0.f;
+    for (int u = tid; u < b.total; u += 256) {   // (each thread reads back what it wrote itself)
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+            if (h >= H) break;
+            const float v = base[(size_t)h * a.ldu + u];
+            const float e = v == -INFINITY ? 0.f : expf(v - top[h]);
+            base[(size_t)h * a.ldu + u] = e;
+            sum[h] += e;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+        const float v = warp_sum(sum[h]);
+        if (lane == 0) red[warp][h] = v;
+    }
+    __syncthreads();
+    if (tid < H) {
+        float v = 0.f;
+        for (int w = 0; w < 8; ++w) v += red[w][tid];
+        if (s.sink) v += expf(s.sink[tid] - top[tid]);
+        a.inv_den[(size_t)(row0 + r - a.row_base) * H + tid] = 1.f / v;
+    }
+}
+
+// pass 3, prompt portions: grid (tiles of the batch, heads); O[64 rows][dv] = sum over the band's 64-key tiles of P V, 4 rows x
+// DV4 float4 column groups a thread
+template <int DV4>
+__global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    extern __shared__ __align__(16) float mixsm[];
+    const int tile = a.tile0 + blockIdx.x, row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1];
+    if (n < a.small) return;
+    const int H = s.heads, dv = s.vdim, dv4 = (dv + 3) / 4 * 4, h = blockIdx.y, g = h / (H / s.kv_heads), ldp = 64 + 4;
+    float* Ps = mixsm;             // [64 rows][ldp]
+    float* Vs = Ps + 64 * ldp;     // [64 keys][dv4]
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const MixBand b = mix_band(m.row_pos[row0], n, s.window, s.keep_first);
+    const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
+    const size_t vstride = (size_t)s.kv_heads * dv;
+    const bool vec = dv % 4 == 0, vecp = a.ldu % 4 == 0;
+    float acc[4][DV4 * 4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < DV4 * 4; ++j) acc[i][j] = 0.f;
+    for (int u0 = 0; u0 < b.total; u0 += 64) {
+        __syncthreads();
+        for (int i = tid; i < 64 * 16; i += 256) {
+            const int r = i >> 4, c4 = (i & 15) * 4;
+            float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < n) {
+                const float* src = a.S + ((size_t)(row0 + r - a.row_base) * H + h) * a.ldu + u0 + c4;
+                if (vecp && u0 + c4 + 3 < b.total) p = *reinterpret_cast<const float4*>(src);
+                else {
+                    if (u0 + c4 < b.total) p.x = src[0];
+                    if (u0 + c4 + 1 < b.total) p.y = src[1];
+                    if (u0 + c4 + 2 < b.total) p.z = src[2];
+                    if (u0 + c4 + 3 < b.total) p.w = src[3];
                 }
-                *reinterpret_cast<float4*>(&Qg[qv * L.ldq + k4]) = v;
             }
-            __syncthreads();
-            for (int qp = ty; 2 * qp < QV; qp += 16) {
-                const int q0 = 2 * qp, q1 = min(q0 + 1, QV - 1);
-                const float* qa = Qg + q0 * L.ldq;
-                const float* qb = Qg + q1 * L.ldq;
-                float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                for (int k = 0; k < L.d4; k += 4) {
-                    const float4 a = *reinterpret_cast<const float4*>(qa + k), b = *reinterpret_cast<const float4*>(qb + k);
+            *reinterpret_cast<float4*>(&Ps[r * ldp + c4]) = p;
+        }
+        for (int i = tid; i < 64 * (dv4 / 4); i += 256) {
+            const int c = i / (dv4 / 4), k4 = (i % (dv4 / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (u0 + c < b.total) {
+                const float* src = v_pool + mix_token(table, b.key(u0 + c)) * vstride + (size_t)g * dv + k4;
+                if (vec) v = *reinterpret_cast<const float4*>(src);
+                else { v.x = src[0]; if (k4 + 1 < dv) v.y = src[1]; if (k4 + 2 < dv) v.z = src[2]; if (k4 + 3 < dv) v.w = src[3]; }
+            }
+            *reinterpret_cast<float4*>(&Vs[c * dv4 + k4]) = v;
+        }
+        __syncthreads();
+        for (int c = 0; c < 64; c += 4) {
+            float4 pr[4];
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const float4 kk = *reinterpret_cast<const float4*>(&KV[(tx + 16 * jj) * L.ldkv + k]);
-                        sc[0][jj] = dot4(a, kk, sc[0][jj]);
-                        sc[1][jj] = dot4(b, kk, sc[1][jj]);
-                    }
-                }
+            for (int i = 0; i < 4; ++i) pr[i] = *reinterpret_cast<const float4*>(&Ps[(ty + 16 * i) * ldp + c]);
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int qv = q0 + i;
-                    if (qv < QV) {
+            for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            float v = sc[i][jj] * s.scale;
-                            if (s.softcap > 0.f) v = s.softcap * tanhf(v * inv_cap);
-                            S[(size_t)(g * QV + qv) * L.ldS + tx + 16 * jj] = v;
+                for (int jj = 0; jj < DV4; ++jj) {
+                    const int col = tx * 4 + 64 * jj;
+                    if (col < dv4) {
+                        const float4 v = *reinterpret_cast<const float4*>(&Vs[(c + cc) * dv4 + col]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float p = cc == 0 ? pr[i].x : cc == 1 ? pr[i].y : cc == 2 ? pr[i].z : pr[i].w;
+                            acc[i][jj * 4 + 0] = fmaf(p, v.x, acc[i][jj * 4 + 0]);
+                            acc[i][jj * 4 + 1] = fmaf(p, v.y, acc[i][jj * 4 + 1]);
+                            acc[i][jj * 4 + 2] = fmaf(p, v.z, acc[i][jj * 4 + 2]);
+                            acc[i][jj * 4 + 3] = fmaf(p, v.w, acc[i][jj * 4 + 3]);
                         }
                     }
                 }
             }
         }
-        __syncthreads();
-        // ---- B: mixing across the heads, mask ----
-        for (int col = tid; col < R * kMixKT; col += 256) {
-            const int r = col / kMixKT, c = col % kMixKT;
-            bool seen = false;
-            if (r < n && c < kc) {
-                const int u = u0 + c, j = u < nA ? u : lo + (u - nA), pos = p0 + r;
-                seen = j <= pos && (s.window <= 0 || pos - j < s.window || j < s.keep_first);
-            }
-            float* sp = S + (size_t)r * L.ldS + c;
-            const size_t hs = (size_t)R * L.ldS;
-            if (!seen) {
-                for (int h = 0; h < H; ++h) sp[h * hs] = -INFINITY;
-            } else if (s.talk) {
-                float sv[HP];
+    }
 #pragma unroll
-                for (int g = 0; g < HP; ++g) sv[g] = g < H ? sp[g * hs] : 0.f;
-                for (int h = 0; h < H; ++h) {
-                    float acc = 0.f;
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+        if (r >= n) continue;
+        const float f = a.inv_den[(size_t)(row0 + r - a.row_base) * H + h];
+        float* o = out + (size_t)(row0 + r) * ((size_t)H * dv) + (size_t)h * dv;
 #pragma unroll
-                    for (int g = 0; g < HP; g += 4) {
-                        const float4 tv = *reinterpret_cast<const float4*>(&Tm[h * HP + g]);
-                        acc = fmaf(tv.x, sv[g], fmaf(tv.y, sv[g + 1], fmaf(tv.z, sv[g + 2], fmaf(tv.w, sv[g + 3], acc))));
-                    }
-                    sp[h * hs] = acc;
-                }
+        for (int jj = 0; jj < DV4; ++jj)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = tx * 4 + 64 * jj + e;
+                if (col < dv) o[col] = acc[i][jj * 4 + e] * f;
             }
+    }
+}
+
+// pass 3, single rows: grid (rows of the batch, heads); 16 warps split the band's keys (four keys in flight a warp), a lane owns the
+// value coordinates lane, lane + 32, ...; the warps' sums are added in warp order
+constexpr int kMixRowWarps = 16;
+template <int PL>
+__global__ void __launch_bounds__(kMixRowWarps * 32) mix_values_rows_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    extern __shared__ __align__(16) float mixsm[];   // [warps][dv]
+    const int row = a.row_base + blockIdx.x, tile = a.row_tile[row], row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1];
+    if (n >= a.small) return;
+    const int H = s.heads, dv = s.vdim, h = blockIdx.y, g = h / (H / s.kv_heads), warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const MixBand b = mix_band(m.row_pos[row0], n, s.window, s.keep_first);
+    const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
+    const size_t vstride = (size_t)s.kv_heads * dv;
+    const float* P = a.S + ((size_t)(row - a.row_base) * H + h) * a.ldu;
+    const int chunk = (b.total + kMixRowWarps - 1) / kMixRowWarps, ub = warp * chunk, ue = min(b.total, ub + chunk);
+    float o[PL];
+#pragma unroll
+    for (int i = 0; i < PL; ++i) o[i] = 0.f;
+    for (int u = ub; u < ue; u += 4) {
+        float p[4];
+        const float* vr[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int uu = min(u + q, ue - 1);
+            p[q] = u + q < ue ? P[uu] : 0.f;
+            vr[q] = v_pool + mix_token(table, b.key(uu)) * vstride + (size_t)g * dv;
         }
-        __syncthreads();
-        // ---- C: running softmax statistics of every (head, row) ----
-        for (int hr = warp; hr < H * R; hr += 8) {
-            float* sp = S + (size_t)hr * L.ldS;
-            const float v0 = sp[lane], v1 = sp[lane + 32];
-            const float tmax = warp_max(fmaxf(v0, v1));
-            const float mo = mrow[hr], nm = fmaxf(mo, tmax);
-            float e0 = 0.f, e1 = 0.f, corr = 1.f;
-            if (nm != -INFINITY) {
-                e0 = expf(v0 - nm);
-                e1 = expf(v1 - nm);
-                corr = expf(mo - nm);
-            }
-            sp[lane] = e0;
-            sp[lane + 32] = e1;
-            const float ps = warp_sum(e0 + e1);
-            if (lane == 0) {
-                lrow[hr] = lrow[hr] * corr + ps;
-                mrow[hr] = nm;
-                crow[hr] = corr;
-            }
+        float vv[4][PL];
+#pragma unroll
+        for (int i = 0; i < PL; ++i) {
+            const int c = lane + 32 * i;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) vv[q][i] = c < dv ? vr[q][c] : 0.f;
         }
-        // ---- D: weighted values ----
-        for (int g = 0; g < G; ++g) {
-            __syncthreads();
-            for (int i = tid; i < kMixKT * (L.dv4 / 4); i += 256) {
-                const int c = i / (L.dv4 / 4), k4 = (i % (L.dv4 / 4)) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (c < kc) {
-                    const int u = u0 + c, j = u < nA ? u : lo + (u - nA);
-                    const float* src = v_pool + ((size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens) * vstride + (size_t)g * dv + k4;
-                    if (vecv) v = *reinterpret_cast<const float4*>(src);
-                    else {
-                        v.x = src[0];
-                        if (k4 + 1 < dv) v.y = src[1];
-                        if (k4 + 2 < dv) v.z = src[2];
-                        if (k4 + 3 < dv) v.w = src[3];
-                    }
-                }
-                *reinterpret_cast<float4*>(&KV[c * L.ldkv + k4]) = v;
-            }
-            __syncthreads();
-            const int ncx = L.dv4 / 4, items = ((QV + 1) / 2) * ncx;
-            for (int item = tid; item < items; item += 256) {
-                const int cx = item % ncx, qp = item / ncx;
-                const int hr0 = g * QV + 2 * qp, hr1 = g * QV + min(2 * qp + 1, QV - 1);
-                const float* pa = S + (size_t)hr0 * L.ldS;
-                const float* pb = S + (size_t)hr1 * L.ldS;
-                float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-                for (int c = 0; c < kc; ++c) {
-                    const float4 v = *reinterpret_cast<const float4*>(&KV[c * L.ldkv + 4 * cx]);
-                    const float x0 = pa[c], x1 = pb[c];
-                    a0.x = fmaf(x0, v.x, a0.x); a0.y = fmaf(x0, v.y, a0.y); a0.z = fmaf(x0, v.z, a0.z); a0.w = fmaf(x0, v.w, a0.w);
-                    a1.x = fmaf(x1, v.x, a1.x); a1.y = fmaf(x1, v.y, a1.y); a1.z = fmaf(x1, v.z, a1.z); a1.w = fmaf(x1, v.w, a1.w);
-                }
-                float4* o0 = reinterpret_cast<float4*>(&O[(size_t)hr0 * L.dv4 + 4 * cx]);
-                const float c0 = crow[hr0];
-                float4 w = *o0;
-                w.x = fmaf(w.x, c0, a0.x); w.y = fmaf(w.y, c0, a0.y); w.z = fmaf(w.z, c0, a0.z); w.w = fmaf(w.w, c0, a0.w);
-                *o0 = w;
-                if (2 * qp + 1 < QV) {
-                    float4* o1 = reinterpret_cast<float4*>(&O[(size_t)hr1 * L.dv4 + 4 * cx]);
-                    const float c1 = crow[hr1];
-                    w = *o1;
-                    w.x = fmaf(w.x, c1, a1.x); w.y = fmaf(w.y, c1, a1.y); w.z = fmaf(w.z, c1, a1.z); w.w = fmaf(w.w, c1, a1.w);
-                    *o1 = w;
-                }
-            }
-        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < PL; ++i) o[i] = fmaf(p[q], vv[q][i], o[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < PL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) mixsm[warp * dv + c] = o[i];
     }
     __syncthreads();
-    if (rows && part) {
-        const size_t ps = (size_t)dv + 2;
-        for (int i = tid; i < H * (dv + 2); i += 256) {
-            const int h = i / (dv + 2), c = i % (dv + 2);
-            const int hr = h * R;
-            float* dst = part + (((size_t)blockIdx.x * H + h) * splits + z) * ps;
-            dst[c] = c == 0 ? mrow[hr] : c == 1 ? lrow[hr] : O[(size_t)hr * L.dv4 + c - 2];
-        }
-    } else {
-        for (int i = tid; i < H * n * dv; i += 256) {
-            const int c = i % dv, r = (i / dv) % n, h = i / (dv * n);
-            const int hr = h * R + r;
-            out[(size_t)(row0 + r) * ((size_t)H * dv) + (size_t)h * dv + c] = O[(size_t)hr * L.dv4 + c] * attn_finish_factor(s, h, mrow[hr], lrow[hr]);
-        }
+    const float f = a.inv_den[(size_t)(row - a.row_base) * H + h];
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float acc = 0.f;
+        for (int w = 0; w < kMixRowWarps; ++w) acc += mixsm[w * dv + c];
+        out[(size_t)row * ((size_t)H * dv) + (size_t)h * dv + c] = acc * f;
     }
 }
 
