@@ -970,7 +970,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         for (int t = 0; t < n_mtiles; ++t) max_total = std::max(max_total, mix_band(h_pos[mtiles[2 * t]], mtiles[2 * t + 1], s.window, s.keep_first).total);
         const int ldu = (max_total + 63) / 64 * 64;
         const size_t per_row = (size_t)H * ldu;
-        const size_t budget_rows = std::max<size_t>(kAttnTile, ((size_t)16 << 20) / per_row);   // 64 MiB of scores
+        const size_t budget_rows = std::max<size_t>(kAttnTile, ((size_t)24 << 20) / per_row);   // 96 MiB of scores: most of them stay in L2 between the passes, and a launch fills the GPU
         for (int t0 = 0; t0 < n_mtiles;) {
             int t1 = t0, rows = 0;
             bool big = false, small = false;
@@ -986,24 +986,31 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.S = m.mix_S.p; a.inv_den = m.mix_den.p;
             const int nt_b = t1 - t0, d4 = (s.dim + 3) / 4 * 4, dv4 = (s.vdim + 3) / 4 * 4;
             if (big) {
-                TRY(launch_dep(mix_scores_tiles_kernel, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 4) * sizeof(float), q, sm, s, a, kp));
+                // bf16 mode: split-TF32 tensor-core products (fp32-accurate); fp32 mode keeps true fp32 arithmetic
+                if (bf && g_use_tc && s.dim % 8 == 0) TRY(launch_dep(mix_scores_tiles_kernel<true>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 4) * sizeof(float), q, sm, s, a, kp));
+                else TRY(launch_dep(mix_scores_tiles_kernel<false>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 4) * sizeof(float), q, sm, s, a, kp));
                 LAUNCHED();
             }
             if (small) {
-                TRY(launch_dep(mix_scores_rows_kernel, dim3(ldu / 64, rows, s.kv_heads), dim3(256), (size_t)HG * s.dim * sizeof(float), q, sm, s, a, kp));
+                TRY(launch_dep(mix_scores_rows_kernel<kAttnMaxPerLane>, dim3(ldu / 64, rows, s.kv_heads), dim3(256), (size_t)HG * s.dim * sizeof(float), q, sm, s, a, kp));
                 LAUNCHED();
             }
             const dim3 g2(big ? kAttnTile : kAttnTiledMinRows - 1, nt_b);
-            if (L.mix_HP == 8) TRY(launch_dep(mix_softmax_kernel<8>, g2, dim3(256), 0, sm, s, a));
-            else if (L.mix_HP == 16) TRY(launch_dep(mix_softmax_kernel<16>, g2, dim3(256), 0, sm, s, a));
-            else if (L.mix_HP == 32) TRY(launch_dep(mix_softmax_kernel<32>, g2, dim3(256), 0, sm, s, a));
-            else TRY(launch_dep(mix_softmax_kernel<64>, g2, dim3(256), 0, sm, s, a));
+            // a row's mixed scores wait in shared memory between the two sweeps when they fit (three blocks an SM), else in the scratch
+            const size_t row_bytes = per_row * sizeof(float);
+            const int in_smem = row_bytes <= 72 * 1024 ? 1 : 0;
+            const size_t sm2 = in_smem ? row_bytes : 0;
+            // (few rows: 512 threads a row have more of its loads in flight; many rows fill the GPU better with 256)
+            if (L.mix_HP == 8 && !big) TRY(launch_dep(mix_softmax_kernel<8, 512>, g2, dim3(512), sm2, sm, s, a, in_smem));
+            else if (L.mix_HP == 16 && !big) TRY(launch_dep(mix_softmax_kernel<16, 512>, g2, dim3(512), sm2, sm, s, a, in_smem));
+            else if (L.mix_HP == 8) TRY(launch_dep(mix_softmax_kernel<8, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
+            else if (L.mix_HP == 16) TRY(launch_dep(mix_softmax_kernel<16, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
+            else if (L.mix_HP == 32) TRY(launch_dep(mix_softmax_kernel<32, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
+            else TRY(launch_dep(mix_softmax_kernel<64, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
             LAUNCHED();
             if (big) {
-                const size_t smem = ((size_t)64 * 68 + (size_t)64 * dv4) * sizeof(float);
-                if (dv4 <= 64) TRY(launch_dep(mix_values_tiles_kernel<1>, dim3(nt_b, H), dim3(256), smem, sm, s, a, vp, out));
-                else if (dv4 <= 128) TRY(launch_dep(mix_values_tiles_kernel<2>, dim3(nt_b, H), dim3(256), smem, sm, s, a, vp, out));
-                else TRY(launch_dep(mix_values_tiles_kernel<4>, dim3(nt_b, H), dim3(256), smem, sm, s, a, vp, out));
+                if (bf && g_use_tc) TRY(launch_dep(mix_values_tiles_kernel<true>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)64 * (68 + 72) * sizeof(float), sm, s, a, vp, out));
+                else TRY(launch_dep(mix_values_tiles_kernel<false>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)64 * (68 + 64) * sizeof(float), sm, s, a, vp, out));
                 LAUNCHED();
             }
             if (small) {
@@ -1039,10 +1046,12 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         }
         const float* mix_in = behind ? m.x.p : m.h.p;   // what the mixer reads
         if (L.d.conv_taps >= 1) {   // ... with the short convolution over the sequence's last inputs added; the slot then keeps the newest ones
-            TRY(launch_dep(short_conv_kernel, dim3(T), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, L.canon, (const float*)R.conv_state.p, m.hc.p));
+            TRY(launch_dep(short_conv_kernel, dim3(T, T <= 64 ? (D + nt - 1) / nt : 1), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, L.canon, R.conv_state.p, m.hc.p));
             LAUNCHED();
-            if (L.d.conv_taps > 1) {
-                TRY(launch_dep(short_conv_save_kernel, dim3(E), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, R.conv_state.p));
+            bool many = false;   // (an entry of one row has shifted its state in the kernel above)
+            for (int e = 0; e < E; ++e) many = many || counts[e] > 1;
+            if (L.d.conv_taps > 1 && many) {
+                TRY(launch_dep(short_conv_save_kernel, dim3(E, (D + nt - 1) / nt), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, R.conv_state.p));
                 LAUNCHED();
             }
             mix_in = m.hc.p;
@@ -1377,11 +1386,15 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<320, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<320>()));
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<192, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<192>()));
     CK(cudaFuncSetAttribute(latent_attention_h3_kernel<160, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<160>()));
-    CK(cudaFuncSetAttribute(mix_scores_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(mix_scores_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(mix_values_tiles_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(mix_values_tiles_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(mix_values_tiles_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_scores_tiles_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_scores_tiles_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_scores_rows_kernel<kAttnMaxPerLane>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_softmax_kernel<8, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    CK(cudaFuncSetAttribute(mix_softmax_kernel<16, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    CK(cudaFuncSetAttribute(mix_softmax_kernel<8, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    CK(cudaFuncSetAttribute(mix_softmax_kernel<16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    CK(cudaFuncSetAttribute(mix_softmax_kernel<32, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    CK(cudaFuncSetAttribute(mix_softmax_kernel<64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     g_device = device;
@@ -1582,7 +1595,8 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             if (L.d.talk || L.d.softcap > 0.f || L.d.keep_first > 0) {
                 const int H = L.d.heads, d4 = (L.d.dim + 3) / 4 * 4, dv4 = (L.d.vdim + 3) / 4 * 4;
                 L.mix_HP = H <= 8 ? 8 : H <= 16 ? 16 : H <= 32 ? 32 : 64;
-                if ((size_t)2 * 64 * (d4 + 4) * sizeof(float) > g_smem_optin || ((size_t)64 * 68 + (size_t)64 * dv4) * sizeof(float) > g_smem_optin)
+                (void)dv4;
+                if ((size_t)2 * 64 * (d4 + 4) * sizeof(float) > g_smem_optin)
                     return fail("finalize: layer %d: head sizes %d / %d do not fit the head-mixing attention's shared memory", i, L.d.dim, L.d.vdim);
                 m.any_mixed = true;
             }

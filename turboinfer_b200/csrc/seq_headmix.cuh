@@ -15,6 +15,7 @@
 //
 // Everything here is fp32 in both compute modes: scores, cap, mixing, softmax and the weighted sum of values.
 #pragma once
+#include "prefill.cuh"
 #include "seq_kernels.cuh"
 
 namespace tib {
@@ -23,12 +24,15 @@ namespace seq {
 // ---- short convolution ------------------------------------------------------------------------------------------------------------
 // state [slots][taps - 1][D]: the inputs at positions len - (taps - 1) .. len - 1 of the slot's sequence, oldest first.  Entries
 // for positions before 0 are never read (a slot that is used again needs no clearing).
-__global__ void short_conv_kernel(const float* x, StepMeta m, int D, int taps, const float* w, const float* state, float* y) {
+// An entry that brings ONE row (a decoded token) also shifts its slot's state here: the thread that read a coordinate's old entries
+// writes its new ones (short_conv_save_kernel then skips that entry).
+__global__ void short_conv_kernel(const float* x, StepMeta m, int D, int taps, const float* w, float* state, float* y) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const int t = blockIdx.x, e = m.row_ent[t], i = t - m.ent_row0[e], pos0 = m.ent_pos0[e];
-    const float* st = state + (size_t)m.ent_slot[e] * (taps - 1) * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float* st = state + (size_t)m.ent_slot[e] * (taps - 1) * D;
+    const bool alone = m.ent_row0[e + 1] - m.ent_row0[e] == 1;
+    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
         const float xv = x[(size_t)t * D + d];
         float acc = xv;
         for (int j = 0; j < taps; ++j) {
@@ -40,6 +44,10 @@ __global__ void short_conv_kernel(const float* x, StepMeta m, int D, int taps, c
             acc = fmaf(w[(size_t)d * taps + j], v, acc);
         }
         y[(size_t)t * D + d] = acc;
+        if (alone) {
+            for (int s = 0; s + 2 < taps; ++s) st[(size_t)s * D + d] = st[(size_t)(s + 1) * D + d];
+            if (taps > 1) st[(size_t)(taps - 2) * D + d] = xv;
+        }
     }
 }
 // after all rows of the step have read the old state: the slot keeps the last taps - 1 inputs of its sequence
@@ -47,8 +55,9 @@ __global__ void short_conv_save_kernel(const float* x, StepMeta m, int D, int ta
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const int e = blockIdx.x, row0 = m.ent_row0[e], n = m.ent_row0[e + 1] - row0;
+    if (n == 1) return;   // (saved by short_conv_kernel)
     float* st = state + (size_t)m.ent_slot[e] * (taps - 1) * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x)
+    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x)
         for (int s = 0; s < taps - 1; ++s) {   // ascending: entry n + s is still the old one when it is read
             const int i = n - (taps - 1) + s;
             st[(size_t)s * D + d] = i >= 0 ? x[(size_t)(row0 + i) * D + d] : st[(size_t)(n + s) * D + d];
@@ -121,7 +130,11 @@ __device__ __forceinline__ float mix_cap(float v, const AttnShape& s) {
 }
 __device__ __forceinline__ size_t mix_token(const int* table, int j) { return (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens; }
 
-// pass 1, prompt portions: grid (band tiles of 64 keys, tiles of the batch, heads)
+// pass 1, prompt portions: grid (band tiles of 64 keys, tiles of the batch, heads).  TC (bf16 mode, head size in whole 8-element
+// steps): the product runs on the warp-level tensor cores at fp32 accuracy -- every fp32 operand is split into two TF32 terms
+// (x = hi + lo) and lo*hi + hi*lo + hi*hi is accumulated in fp32 by mma.sync m16n8k8; a warp owns 16 rows x 32 keys.  Otherwise
+// true fp32 multiply-adds, 4 rows x 4 keys a thread.
+template <bool TC>
 __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv, StepMeta m, AttnShape s, MixArgs a, const float* k_pool) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
@@ -156,6 +169,43 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
         *reinterpret_cast<float4*>(&Ks[r * ldq + k4]) = k;
     }
     __syncthreads();
+    if constexpr (TC) {
+        const int warp = tid >> 5, lane = tid & 31, gg = lane >> 2, t = lane & 3, rg = warp & 3, kh = warp >> 2;
+        float c[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+        const float* qa = Qs + (16 * rg + gg) * ldq + t;
+        const float* kb = Ks + (32 * kh + gg) * ldq + t;
+        for (int k0 = 0; k0 < d4; k0 += 8) {
+            uint32_t ah[4], al[4];
+            split_tf32(qa[k0], ah[0], al[0]);
+            split_tf32(qa[8 * ldq + k0], ah[1], al[1]);
+            split_tf32(qa[k0 + 4], ah[2], al[2]);
+            split_tf32(qa[8 * ldq + k0 + 4], ah[3], al[3]);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                uint32_t bh0, bl0, bh1, bl1;
+                split_tf32(kb[8 * nt * ldq + k0], bh0, bl0);
+                split_tf32(kb[8 * nt * ldq + k0 + 4], bh1, bl1);
+                mma_tf32(c[nt], al, bh0, bh1);
+                mma_tf32(c[nt], ah, bl0, bl1);
+                mma_tf32(c[nt], ah, bh0, bh1);
+            }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = 16 * rg + gg + 8 * half;
+            if (r >= n) continue;
+            float* dst = a.S + ((size_t)(row0 + r - a.row_base) * s.heads + h) * a.ldu + u0;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int key = 32 * kh + 8 * nt + 2 * t;
+                if (u0 + key < b.total) dst[key] = mix_cap(c[nt][2 * half], s);
+                if (u0 + key + 1 < b.total) dst[key + 1] = mix_cap(c[nt][2 * half + 1], s);
+            }
+        }
+        return;
+    }
     float sc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -186,6 +236,7 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
 
 // pass 1, single rows: grid (chunks of 64 keys, rows of the batch, key/value heads); a warp takes 8 keys, a lane the coordinates
 // lane, lane + 32, ...; the row's query heads of the group wait in shared memory
+template <int PL>   // coordinates of a head a lane owns: head sizes up to 32 * PL
 __global__ void __launch_bounds__(256) mix_scores_rows_kernel(const float* qkv, StepMeta m, AttnShape s, MixArgs a, const float* k_pool) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
@@ -200,22 +251,33 @@ __global__ void __launch_bounds__(256) mix_scores_rows_kernel(const float* qkv, 
     __syncthreads();
     const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
     const size_t kstride = (size_t)s.kv_heads * d;
-    for (int c = 0; c < 8; ++c) {
-        const int u = u0 + warp * 8 + c;
-        if (u >= b.total) break;
-        const float* kr = k_pool + mix_token(table, b.key(u)) * kstride + (size_t)g * d;
-        for (int hl0 = 0; hl0 < HG; hl0 += 4) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int k = lane; k < d; k += 32) {
-                const float kv = kr[k];
+    // the warp's 8 key rows are requested together (PL coordinates a lane each), then multiplied with four query heads at a time
+    float kv[8][PL];
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    if (hl0 + q < HG) acc[q] = fmaf(mixsm[(hl0 + q) * d + k], kv, acc[q]);
-            }
+    for (int c = 0; c < 8; ++c) {
+        const int u = min(u0 + warp * 8 + c, b.total - 1);
+        const float* kr = k_pool + mix_token(table, b.key(u)) * kstride + (size_t)g * d;
+#pragma unroll
+        for (int i = 0; i < PL; ++i) kv[c][i] = lane + 32 * i < d ? kr[lane + 32 * i] : 0.f;
+    }
+    for (int hl0 = 0; hl0 < HG; hl0 += 4) {
+        float qv[4][PL];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < PL; ++i) qv[q][i] = (hl0 + q < HG && lane + 32 * i < d) ? mixsm[(hl0 + q) * d + lane + 32 * i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int u = u0 + warp * 8 + c;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < PL; ++i)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[q] = fmaf(qv[q][i], kv[c][i], acc[q]);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float v = warp_sum(acc[q]);
-                if (lane == 0 && hl0 + q < HG) a.S[((size_t)(row - a.row_base) * s.heads + g * HG + hl0 + q) * a.ldu + u] = mix_cap(v, s);
+                if (lane == 0 && hl0 + q < HG && u < b.total) a.S[((size_t)(row - a.row_base) * s.heads + g * HG + hl0 + q) * a.ldu + u] = mix_cap(v, s);
             }
         }
     }
@@ -223,12 +285,13 @@ __global__ void __launch_bounds__(256) mix_scores_rows_kernel(const float* qkv, 
 
 // pass 2: grid (64, tiles of the batch); block (r, tile) owns row r of the tile and all heads: every key's H scores are mixed in
 // registers and masked, then every head's weights exp(s - max) replace its scores and 1 / (their sum + exp(sink - max)) is kept
-template <int HP>
-__global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape s, MixArgs a) {
+template <int HP, int NT>   // NT threads: 512 where the heads' registers allow it (more of a row's loads in flight), else 256
+__global__ void __launch_bounds__(NT) mix_softmax_kernel(StepMeta m, AttnShape s, MixArgs a, int in_smem) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
+    extern __shared__ __align__(16) float mixsm[];   // in_smem: [H][ldu] the row's mixed scores between the two sweeps
     __shared__ __align__(16) float Tm[HP * HP];
-    __shared__ float red[8][HP];
+    __shared__ float red[NT / 32][HP];
     __shared__ float top[HP];
     const int tile = a.tile0 + blockIdx.y, row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1], r = blockIdx.x;
     if (r >= n) return;
@@ -236,13 +299,13 @@ __global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape 
     const int p0 = m.row_pos[row0], pos = p0 + r;
     const MixBand b = mix_band(p0, n, s.window, s.keep_first);
     if (s.talk)
-        for (int i = tid; i < HP * HP; i += 256) Tm[i] = (i / HP < H && i % HP < H) ? s.talk[(i / HP) * H + i % HP] : 0.f;
+        for (int i = tid; i < HP * HP; i += NT) Tm[i] = (i / HP < H && i % HP < H) ? s.talk[(i / HP) * H + i % HP] : 0.f;
     __syncthreads();
     float* base = a.S + (size_t)(row0 + r - a.row_base) * H * a.ldu;
     float mx[HP];
 #pragma unroll
     for (int h = 0; h < HP; ++h) mx[h] = -INFINITY;
-    for (int u = tid; u < b.total; u += 256) {
+    for (int u = tid; u < b.total; u += NT) {
         const int j = b.key(u);
         const bool seen = j <= pos && (s.window <= 0 || pos - j < s.window || j < s.keep_first);
         float sv[HP];
@@ -261,7 +324,8 @@ __global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape 
                 }
             }
             v = seen ? v : -INFINITY;
-            base[(size_t)h * a.ldu + u] = v;
+            if (in_smem) mixsm[(size_t)h * a.ldu + u] = v;
+            else base[(size_t)h * a.ldu + u] = v;
             mx[h] = fmaxf(mx[h], v);
         }
     }
@@ -273,7 +337,7 @@ __global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape 
     __syncthreads();
     if (tid < HP) {
         float v = red[0][tid];
-        for (int w = 1; w < 8; ++w) v = fmaxf(v, red[w][tid]);
+        for (int w = 1; w < NT / 32; ++w) v = fmaxf(v, red[w][tid]);
         if (s.sink && tid < H) v = fmaxf(v, s.sink[tid]);
         top[tid] = v;
     }
@@ -281,11 +345,11 @@ __global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape 
     float sum[HP];
 #pragma unroll
     for (int h = 0; h < HP; ++h) sum[h] = 0.f;
-    for (int u = tid; u < b.total; u += 256) {   // (each thread reads back what it wrote itself)
+    for (int u = tid; u < b.total; u += NT) {   // (each thread reads back what it wrote itself)
 #pragma unroll
         for (int h = 0; h < HP; ++h) {
             if (h >= H) break;
-            const float v = base[(size_t)h * a.ldu + u];
+            const float v = in_smem ? mixsm[(size_t)h * a.ldu + u] : base[(size_t)h * a.ldu + u];
             const float e = v == -INFINITY ? 0.f : expf(v - top[h]);
             base[(size_t)h * a.ldu + u] = e;
             sum[h] += e;
@@ -300,39 +364,45 @@ __global__ void __launch_bounds__(256) mix_softmax_kernel(StepMeta m, AttnShape 
     __syncthreads();
     if (tid < H) {
         float v = 0.f;
-        for (int w = 0; w < 8; ++w) v += red[w][tid];
+        for (int w = 0; w < NT / 32; ++w) v += red[w][tid];
         if (s.sink) v += expf(s.sink[tid] - top[tid]);
         a.inv_den[(size_t)(row0 + r - a.row_base) * H + tid] = 1.f / v;
     }
 }
 
-// pass 3, prompt portions: grid (tiles of the batch, heads); O[64 rows][dv] = sum over the band's 64-key tiles of P V, 4 rows x
-// DV4 float4 column groups a thread
-template <int DV4>
+// pass 3, prompt portions: grid (tiles of the batch, heads, groups of 64 value columns); O[64 rows][64 columns] = sum over the band's
+// 64-key tiles of P V, 4 rows x 4 columns a thread -- or, TC (bf16 mode), split-TF32 tensor-core products as in pass 1, a warp owning
+// 16 rows x 32 columns
+template <bool TC>
 __global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     extern __shared__ __align__(16) float mixsm[];
     const int tile = a.tile0 + blockIdx.x, row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1];
     if (n < a.small) return;
-    const int H = s.heads, dv = s.vdim, dv4 = (dv + 3) / 4 * 4, h = blockIdx.y, g = h / (H / s.kv_heads), ldp = 64 + 4;
+    const int H = s.heads, dv = s.vdim, h = blockIdx.y, g = h / (H / s.kv_heads), ldp = 64 + 4;
     float* Ps = mixsm;             // [64 rows][ldp]
-    float* Vs = Ps + 64 * ldp;     // [64 keys][dv4]
+    constexpr int ldv = TC ? 72 : 64;   // (the tensor-core fragments read four key rows at once: a stride of 72 keeps them in different banks)
+    float* Vs = Ps + 64 * ldp;     // [64 keys][ldv]
+    const int col0 = blockIdx.z * 64;
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int warp = tid >> 5, lane = tid & 31, gg = lane >> 2, t4 = lane & 3, rg = warp & 3, ch = warp >> 2;
     const MixBand b = mix_band(m.row_pos[row0], n, s.window, s.keep_first);
     const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
     const size_t vstride = (size_t)s.kv_heads * dv;
     const bool vec = dv % 4 == 0, vecp = a.ldu % 4 == 0;
-    float acc[4][DV4 * 4];
+    float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < DV4 * 4; ++j) acc[i][j] = 0.f;
-    for (int u0 = 0; u0 < b.total; u0 += 64) {
-        __syncthreads();
-        for (int i = tid; i < 64 * 16; i += 256) {
-            const int r = i >> 4, c4 = (i & 15) * 4;
-            float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    // the next key tile's weights and values are requested while the current one is multiplied (four 16-byte loads of each a thread)
+    float4 np[4], nv[4];
+    const auto fetch = [&](int u0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i = tid + 256 * q, r = i >> 4, c4 = (i & 15) * 4;
+            float4 p = make_float4(0.f, 0.f, 0.f, 0.f), v = p;
             if (r < n) {
                 const float* src = a.S + ((size_t)(row0 + r - a.row_base) * H + h) * a.ldu + u0 + c4;
                 if (vecp && u0 + c4 + 3 < b.total) p = *reinterpret_cast<const float4*>(src);
@@ -343,42 +413,82 @@ __global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnS
                     if (u0 + c4 + 3 < b.total) p.w = src[3];
                 }
             }
-            *reinterpret_cast<float4*>(&Ps[r * ldp + c4]) = p;
-        }
-        for (int i = tid; i < 64 * (dv4 / 4); i += 256) {
-            const int c = i / (dv4 / 4), k4 = (i % (dv4 / 4)) * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (u0 + c < b.total) {
-                const float* src = v_pool + mix_token(table, b.key(u0 + c)) * vstride + (size_t)g * dv + k4;
+            const int k4 = col0 + c4;   // (r is the key of the tile here)
+            if (u0 + r < b.total && k4 < dv) {
+                const float* src = v_pool + mix_token(table, b.key(u0 + r)) * vstride + (size_t)g * dv + k4;
                 if (vec) v = *reinterpret_cast<const float4*>(src);
                 else { v.x = src[0]; if (k4 + 1 < dv) v.y = src[1]; if (k4 + 2 < dv) v.z = src[2]; if (k4 + 3 < dv) v.w = src[3]; }
             }
-            *reinterpret_cast<float4*>(&Vs[c * dv4 + k4]) = v;
+            np[q] = p;
+            nv[q] = v;
+        }
+    };
+    fetch(0);
+    for (int u0 = 0; u0 < b.total; u0 += 64) {
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i = tid + 256 * q, r = i >> 4, c4 = (i & 15) * 4;
+            *reinterpret_cast<float4*>(&Ps[r * ldp + c4]) = np[q];
+            *reinterpret_cast<float4*>(&Vs[r * ldv + c4]) = nv[q];
         }
         __syncthreads();
+        if (u0 + 64 < b.total) fetch(u0 + 64);
+        if constexpr (TC) {
+            const float* pa = Ps + (16 * rg + gg) * ldp + t4;
+            const float* vb = Vs + t4 * ldv + 32 * ch + gg;
+#pragma unroll 2
+            for (int k0 = 0; k0 < 64; k0 += 8) {
+                uint32_t ah[4], al[4];
+                split_tf32(pa[k0], ah[0], al[0]);
+                split_tf32(pa[8 * ldp + k0], ah[1], al[1]);
+                split_tf32(pa[k0 + 4], ah[2], al[2]);
+                split_tf32(pa[8 * ldp + k0 + 4], ah[3], al[3]);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    uint32_t bh0, bl0, bh1, bl1;
+                    split_tf32(vb[k0 * ldv + 8 * nt], bh0, bl0);
+                    split_tf32(vb[(k0 + 4) * ldv + 8 * nt], bh1, bl1);
+                    mma_tf32(acc[nt], al, bh0, bh1);
+                    mma_tf32(acc[nt], ah, bl0, bl1);
+                    mma_tf32(acc[nt], ah, bh0, bh1);
+                }
+            }
+            continue;
+        }
         for (int c = 0; c < 64; c += 4) {
             float4 pr[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) pr[i] = *reinterpret_cast<const float4*>(&Ps[(ty + 16 * i) * ldp + c]);
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
+                const float4 v = *reinterpret_cast<const float4*>(&Vs[(c + cc) * ldv + tx * 4]);
 #pragma unroll
-                for (int jj = 0; jj < DV4; ++jj) {
-                    const int col = tx * 4 + 64 * jj;
-                    if (col < dv4) {
-                        const float4 v = *reinterpret_cast<const float4*>(&Vs[(c + cc) * dv4 + col]);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float p = cc == 0 ? pr[i].x : cc == 1 ? pr[i].y : cc == 2 ? pr[i].z : pr[i].w;
-                            acc[i][jj * 4 + 0] = fmaf(p, v.x, acc[i][jj * 4 + 0]);
-                            acc[i][jj * 4 + 1] = fmaf(p, v.y, acc[i][jj * 4 + 1]);
-                            acc[i][jj * 4 + 2] = fmaf(p, v.z, acc[i][jj * 4 + 2]);
-                            acc[i][jj * 4 + 3] = fmaf(p, v.w, acc[i][jj * 4 + 3]);
-                        }
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const float p = cc == 0 ? pr[i].x : cc == 1 ? pr[i].y : cc == 2 ? pr[i].z : pr[i].w;
+                    acc[i][0] = fmaf(p, v.x, acc[i][0]);
+                    acc[i][1] = fmaf(p, v.y, acc[i][1]);
+                    acc[i][2] = fmaf(p, v.z, acc[i][2]);
+                    acc[i][3] = fmaf(p, v.w, acc[i][3]);
                 }
             }
         }
+    }
+    if constexpr (TC) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = 16 * rg + gg + 8 * half;
+            if (r >= n) continue;
+            const float f = a.inv_den[(size_t)(row0 + r - a.row_base) * H + h];
+            float* o = out + (size_t)(row0 + r) * ((size_t)H * dv) + (size_t)h * dv;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int col = col0 + 32 * ch + 8 * nt + 2 * t4;
+                if (col < dv) o[col] = acc[nt][2 * half] * f;
+                if (col + 1 < dv) o[col + 1] = acc[nt][2 * half + 1] * f;
+            }
+        }
+        return;
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -387,18 +497,16 @@ __global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnS
         const float f = a.inv_den[(size_t)(row0 + r - a.row_base) * H + h];
         float* o = out + (size_t)(row0 + r) * ((size_t)H * dv) + (size_t)h * dv;
 #pragma unroll
-        for (int jj = 0; jj < DV4; ++jj)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int col = tx * 4 + 64 * jj + e;
-                if (col < dv) o[col] = acc[i][jj * 4 + e] * f;
-            }
+        for (int e = 0; e < 4; ++e) {
+            const int col = col0 + tx * 4 + e;
+            if (col < dv) o[col] = acc[i][e] * f;
+        }
     }
 }
 
-// pass 3, single rows: grid (rows of the batch, heads); 16 warps split the band's keys (four keys in flight a warp), a lane owns the
+// pass 3, single rows: grid (rows of the batch, heads); 32 warps split the band's keys (four keys in flight a warp), a lane owns the
 // value coordinates lane, lane + 32, ...; the warps' sums are added in warp order
-constexpr int kMixRowWarps = 16;
+constexpr int kMixRowWarps = 32;
 template <int PL>
 __global__ void __launch_bounds__(kMixRowWarps * 32) mix_values_rows_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
     pdl_launch_dependents();
