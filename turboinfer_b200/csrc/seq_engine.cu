@@ -986,9 +986,9 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.S = m.mix_S.p; a.inv_den = m.mix_den.p;
             const int nt_b = t1 - t0, d4 = (s.dim + 3) / 4 * 4, dv4 = (s.vdim + 3) / 4 * 4;
             if (big) {
-                // bf16 mode: split-TF32 tensor-core products (fp32-accurate); fp32 mode keeps true fp32 arithmetic
-                if (bf && g_use_tc && s.dim % 8 == 0) TRY(launch_dep(mix_scores_tiles_kernel<true>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 4) * sizeof(float), q, sm, s, a, kp));
-                else TRY(launch_dep(mix_scores_tiles_kernel<false>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 4) * sizeof(float), q, sm, s, a, kp));
+                // bf16 mode: split-half tensor-core products (fp32-accurate); fp32 mode keeps true fp32 arithmetic
+                if (bf && g_use_tc && s.dim % 16 == 0) TRY(launch_dep(mix_scores_tiles_kernel<true>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 8) * sizeof(float), q, sm, s, a, kp));
+                else TRY(launch_dep(mix_scores_tiles_kernel<false>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 8) * sizeof(float), q, sm, s, a, kp));
                 LAUNCHED();
             }
             if (small) {
@@ -1009,7 +1009,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             else TRY(launch_dep(mix_softmax_kernel<64, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
             LAUNCHED();
             if (big) {
-                if (bf && g_use_tc) TRY(launch_dep(mix_values_tiles_kernel<true>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)64 * (68 + 72) * sizeof(float), sm, s, a, vp, out));
+                if (bf && g_use_tc) TRY(launch_dep(mix_values_tiles_kernel<true>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)4 * 64 * 72 * sizeof(__half), sm, s, a, vp, out));
                 else TRY(launch_dep(mix_values_tiles_kernel<false>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)64 * (68 + 64) * sizeof(float), sm, s, a, vp, out));
                 LAUNCHED();
             }
@@ -1596,7 +1596,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
                 const int H = L.d.heads, d4 = (L.d.dim + 3) / 4 * 4, dv4 = (L.d.vdim + 3) / 4 * 4;
                 L.mix_HP = H <= 8 ? 8 : H <= 16 ? 16 : H <= 32 ? 32 : 64;
                 (void)dv4;
-                if ((size_t)2 * 64 * (d4 + 4) * sizeof(float) > g_smem_optin)
+                if ((size_t)2 * 64 * (d4 + 8) * sizeof(float) > g_smem_optin)
                     return fail("finalize: layer %d: head sizes %d / %d do not fit the head-mixing attention's shared memory", i, L.d.dim, L.d.vdim);
                 m.any_mixed = true;
             }

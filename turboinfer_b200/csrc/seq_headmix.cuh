@@ -130,10 +130,10 @@ __device__ __forceinline__ float mix_cap(float v, const AttnShape& s) {
 }
 __device__ __forceinline__ size_t mix_token(const int* table, int j) { return (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens; }
 
-// pass 1, prompt portions: grid (band tiles of 64 keys, tiles of the batch, heads).  TC (bf16 mode, head size in whole 8-element
-// steps): the product runs on the warp-level tensor cores at fp32 accuracy -- every fp32 operand is split into two TF32 terms
-// (x = hi + lo) and lo*hi + hi*lo + hi*hi is accumulated in fp32 by mma.sync m16n8k8; a warp owns 16 rows x 32 keys.  Otherwise
-// true fp32 multiply-adds, 4 rows x 4 keys a thread.
+// pass 1, prompt portions: grid (band tiles of 64 keys, tiles of the batch, heads).  TC (bf16 mode, head size in whole 16-element
+// steps): the product runs on the warp-level tensor cores at fp32 accuracy, the split-half scheme of window_attention_h3_kernel --
+// every fp32 operand is split into two fp16 halves (x = hi + lo) as it is staged, and lo*hi + hi*lo + hi*hi is accumulated in fp32
+// by mma.sync m16n8k16; a warp owns 16 rows x 32 keys.  Otherwise true fp32 multiply-adds, 4 rows x 4 keys a thread.
 template <bool TC>
 __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv, StepMeta m, AttnShape s, MixArgs a, const float* k_pool) {
     pdl_launch_dependents();
@@ -148,6 +148,18 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
     const int d = s.dim, d4 = (d + 3) / 4 * 4, ldq = d4 + 4, h = blockIdx.z, g = h / (s.heads / s.kv_heads);
     float* Qs = mixsm;
     float* Ks = Qs + 64 * ldq;
+    // TC: four fp16 images [64][d + 8] (hi and lo halves of the queries and of the keys) in the same bytes
+    const int LD = d + 8;
+    __half* Qh = reinterpret_cast<__half*>(mixsm);
+    __half* Ql = Qh + 64 * LD;
+    __half* Kh = Ql + 64 * LD;
+    __half* Kl = Kh + 64 * LD;
+    const auto store_split4 = [](const float4& v, __half* hi, __half* lo) {
+        __half x[4], y[4];
+        split_h(v.x, x[0], y[0]); split_h(v.y, x[1], y[1]); split_h(v.z, x[2], y[2]); split_h(v.w, x[3], y[3]);
+        *reinterpret_cast<uint2*>(hi) = make_uint2(pack_h2(x[0], x[1]), pack_h2(x[2], x[3]));
+        *reinterpret_cast<uint2*>(lo) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
+    };
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
     const size_t kstride = (size_t)s.kv_heads * d;
@@ -165,8 +177,13 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
             if (vec) k = *reinterpret_cast<const float4*>(src);
             else { k.x = src[0]; if (k4 + 1 < d) k.y = src[1]; if (k4 + 2 < d) k.z = src[2]; if (k4 + 3 < d) k.w = src[3]; }
         }
-        *reinterpret_cast<float4*>(&Qs[r * ldq + k4]) = q;
-        *reinterpret_cast<float4*>(&Ks[r * ldq + k4]) = k;
+        if constexpr (TC) {
+            store_split4(q, Qh + r * LD + k4, Ql + r * LD + k4);
+            store_split4(k, Kh + r * LD + k4, Kl + r * LD + k4);
+        } else {
+            *reinterpret_cast<float4*>(&Qs[r * ldq + k4]) = q;
+            *reinterpret_cast<float4*>(&Ks[r * ldq + k4]) = k;
+        }
     }
     __syncthreads();
     if constexpr (TC) {
@@ -174,22 +191,26 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
         float c[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
-        const float* qa = Qs + (16 * rg + gg) * ldq + t;
-        const float* kb = Ks + (32 * kh + gg) * ldq + t;
-        for (int k0 = 0; k0 < d4; k0 += 8) {
-            uint32_t ah[4], al[4];
-            split_tf32(qa[k0], ah[0], al[0]);
-            split_tf32(qa[8 * ldq + k0], ah[1], al[1]);
-            split_tf32(qa[k0 + 4], ah[2], al[2]);
-            split_tf32(qa[8 * ldq + k0 + 4], ah[3], al[3]);
+        const uint32_t* qh_row = reinterpret_cast<const uint32_t*>(Qh + (16 * rg + gg) * LD) + t;
+        const uint32_t* ql_row = reinterpret_cast<const uint32_t*>(Ql + (16 * rg + gg) * LD) + t;
+        const int lm = lane >> 3, lr = lane & 7;
+        const uint32_t k_ld = (uint32_t)(((lr + 8 * (lm >> 1)) * LD + 8 * (lm & 1)) * 2);
+        const uint32_t kh_s = smem_u32(Kh), kl_s = smem_u32(Kl);
+        for (int ks = 0; ks < d / 16; ++ks) {
+            const uint32_t ah[4] = {qh_row[8 * ks], qh_row[8 * ks + 4 * LD], qh_row[8 * ks + 4], qh_row[8 * ks + 4 * LD + 4]};
+            const uint32_t al[4] = {ql_row[8 * ks], ql_row[8 * ks + 4 * LD], ql_row[8 * ks + 4], ql_row[8 * ks + 4 * LD + 4]};
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                uint32_t bh0, bl0, bh1, bl1;
-                split_tf32(kb[8 * nt * ldq + k0], bh0, bl0);
-                split_tf32(kb[8 * nt * ldq + k0 + 4], bh1, bl1);
-                mma_tf32(c[nt], al, bh0, bh1);
-                mma_tf32(c[nt], ah, bl0, bl1);
-                mma_tf32(c[nt], ah, bh0, bh1);
+            for (int jp = 0; jp < 2; ++jp) {
+                uint32_t bh[4], bl[4];
+                const uint32_t off = (uint32_t)(((32 * kh + 16 * jp) * LD + 16 * ks) * 2) + k_ld;
+                ldsm_x4(bh, kh_s + off);
+                ldsm_x4(bl, kl_s + off);
+                mma_f16(c[2 * jp], al, bh[0], bh[1]);
+                mma_f16(c[2 * jp + 1], al, bh[2], bh[3]);
+                mma_f16(c[2 * jp], ah, bl[0], bl[1]);
+                mma_f16(c[2 * jp + 1], ah, bl[2], bl[3]);
+                mma_f16(c[2 * jp], ah, bh[0], bh[1]);
+                mma_f16(c[2 * jp + 1], ah, bh[2], bh[3]);
             }
         }
 #pragma unroll
@@ -371,8 +392,8 @@ __global__ void __launch_bounds__(NT) mix_softmax_kernel(StepMeta m, AttnShape s
 }
 
 // pass 3, prompt portions: grid (tiles of the batch, heads, groups of 64 value columns); O[64 rows][64 columns] = sum over the band's
-// 64-key tiles of P V, 4 rows x 4 columns a thread -- or, TC (bf16 mode), split-TF32 tensor-core products as in pass 1, a warp owning
-// 16 rows x 32 columns
+// 64-key tiles of P V, 4 rows x 4 columns a thread -- or, TC (bf16 mode), split-half tensor-core products as in pass 1 (the value tile
+// is read through transposing matrix loads), a warp owning 16 rows x 32 columns
 template <bool TC>
 __global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
     pdl_launch_dependents();
@@ -382,8 +403,20 @@ __global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnS
     if (n < a.small) return;
     const int H = s.heads, dv = s.vdim, h = blockIdx.y, g = h / (H / s.kv_heads), ldp = 64 + 4;
     float* Ps = mixsm;             // [64 rows][ldp]
-    constexpr int ldv = TC ? 72 : 64;   // (the tensor-core fragments read four key rows at once: a stride of 72 keeps them in different banks)
+    constexpr int ldv = 64;
     float* Vs = Ps + 64 * ldp;     // [64 keys][ldv]
+    // TC: four fp16 images [64][72] (hi and lo halves of the weights and of the values)
+    constexpr int LH = 72;
+    __half* Ph = reinterpret_cast<__half*>(mixsm);
+    __half* Pl = Ph + 64 * LH;
+    __half* Vh = Pl + 64 * LH;
+    __half* Vl = Vh + 64 * LH;
+    const auto store_split4 = [](const float4& v, __half* hi, __half* lo) {
+        __half x[4], y[4];
+        split_h(v.x, x[0], y[0]); split_h(v.y, x[1], y[1]); split_h(v.z, x[2], y[2]); split_h(v.w, x[3], y[3]);
+        *reinterpret_cast<uint2*>(hi) = make_uint2(pack_h2(x[0], x[1]), pack_h2(x[2], x[3]));
+        *reinterpret_cast<uint2*>(lo) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
+    };
     const int col0 = blockIdx.z * 64;
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int warp = tid >> 5, lane = tid & 31, gg = lane >> 2, t4 = lane & 3, rg = warp & 3, ch = warp >> 2;
@@ -429,29 +462,38 @@ __global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnS
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int i = tid + 256 * q, r = i >> 4, c4 = (i & 15) * 4;
-            *reinterpret_cast<float4*>(&Ps[r * ldp + c4]) = np[q];
-            *reinterpret_cast<float4*>(&Vs[r * ldv + c4]) = nv[q];
+            if constexpr (TC) {
+                store_split4(np[q], Ph + r * LH + c4, Pl + r * LH + c4);
+                store_split4(nv[q], Vh + r * LH + c4, Vl + r * LH + c4);
+            } else {
+                *reinterpret_cast<float4*>(&Ps[r * ldp + c4]) = np[q];
+                *reinterpret_cast<float4*>(&Vs[r * ldv + c4]) = nv[q];
+            }
         }
         __syncthreads();
         if (u0 + 64 < b.total) fetch(u0 + 64);
         if constexpr (TC) {
-            const float* pa = Ps + (16 * rg + gg) * ldp + t4;
-            const float* vb = Vs + t4 * ldv + 32 * ch + gg;
-#pragma unroll 2
-            for (int k0 = 0; k0 < 64; k0 += 8) {
-                uint32_t ah[4], al[4];
-                split_tf32(pa[k0], ah[0], al[0]);
-                split_tf32(pa[8 * ldp + k0], ah[1], al[1]);
-                split_tf32(pa[k0 + 4], ah[2], al[2]);
-                split_tf32(pa[8 * ldp + k0 + 4], ah[3], al[3]);
+            const uint32_t* ph_row = reinterpret_cast<const uint32_t*>(Ph + (16 * rg + gg) * LH) + t4;
+            const uint32_t* pl_row = reinterpret_cast<const uint32_t*>(Pl + (16 * rg + gg) * LH) + t4;
+            const int lm = lane >> 3, lr = lane & 7;
+            const uint32_t v_ld = (uint32_t)(((lr + 8 * (lm & 1)) * LH + 8 * (lm >> 1)) * 2);
+            const uint32_t vh_s = smem_u32(Vh), vl_s = smem_u32(Vl);
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    uint32_t bh0, bl0, bh1, bl1;
-                    split_tf32(vb[k0 * ldv + 8 * nt], bh0, bl0);
-                    split_tf32(vb[(k0 + 4) * ldv + 8 * nt], bh1, bl1);
-                    mma_tf32(acc[nt], al, bh0, bh1);
-                    mma_tf32(acc[nt], ah, bl0, bl1);
-                    mma_tf32(acc[nt], ah, bh0, bh1);
+            for (int kk = 0; kk < 4; ++kk) {
+                const uint32_t ah[4] = {ph_row[8 * kk], ph_row[8 * kk + 4 * LH], ph_row[8 * kk + 4], ph_row[8 * kk + 4 * LH + 4]};
+                const uint32_t al[4] = {pl_row[8 * kk], pl_row[8 * kk + 4 * LH], pl_row[8 * kk + 4], pl_row[8 * kk + 4 * LH + 4]};
+#pragma unroll
+                for (int np2 = 0; np2 < 2; ++np2) {
+                    uint32_t bh[4], bl[4];
+                    const uint32_t off = (uint32_t)((16 * kk * LH + 32 * ch + 16 * np2) * 2) + v_ld;
+                    ldsm_x4_trans(bh, vh_s + off);
+                    ldsm_x4_trans(bl, vl_s + off);
+                    mma_f16(acc[2 * np2], al, bh[0], bh[1]);
+                    mma_f16(acc[2 * np2 + 1], al, bh[2], bh[3]);
+                    mma_f16(acc[2 * np2], ah, bl[0], bl[1]);
+                    mma_f16(acc[2 * np2 + 1], ah, bl[2], bl[3]);
+                    mma_f16(acc[2 * np2], ah, bh[0], bh[1]);
+                    mma_f16(acc[2 * np2 + 1], ah, bh[2], bh[3]);
                 }
             }
             continue;
