@@ -49,6 +49,7 @@ MECHANISMS = {
     "as_many_key_value_heads": make_config([layer(heads=4, kv_heads=4, dim=8, vdim=8, window=30, keep=2)]),
     "nine_heads": make_config([layer(heads=9, kv_heads=3, dim=8, vdim=12, window=40, keep=1)], width=64),
     "twenty_heads": make_config([layer(heads=20, kv_heads=5, dim=4, vdim=4, window=33, keep=4)], width=40),
+    "forty_heads": make_config([layer(heads=40, kv_heads=8, dim=4, vdim=8, window=21, keep=2)], width=40),
     "window_one": make_config([layer(window=1, keep=0), layer(window=1, keep=2)]),
     "window_beyond_the_sequence": make_config([layer(window=500, keep=7)]),
     "kept_prefix_longer_than_window": make_config([layer(window=4, keep=11)]),
@@ -293,6 +294,20 @@ def test_convolution_state_crosses_every_cut():
         got = run_schedule(m, {"a": toks}, [[("a", n)] for n in sizes])["a"]
         assert rel_err(got, want) < TOL["float32"], sizes
     m.free()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_window_many_heads(dtype):
+    """20 heads over a window of 900 keys: a row's scores of all heads (20 x 960 numbers) no longer fit the shared memory of the
+    mixing pass, which then keeps them in the score scratch between its two sweeps; prompt tiles and decoded rows."""
+    cfg = make_config([layer(heads=20, kv_heads=4, dim=16, vdim=8, window=900, keep=3, mlp=dense(32))], width=40)
+    W = random_weights(cfg, seed=23)
+    toks = tokens(1000, cfg["vocab"], 9)
+    want, _ = plain.run(cfg, W, toks)
+    m = build_engine(cfg, W, dtype, max_tokens=1024)
+    got = run_schedule(m, {"a": toks}, [[("a", 700)], [("a", 3)], [("a", 290)]] + [[("a", 1)]] * 7)["a"]
+    m.free()
+    assert rel_err(got, want) < TOL[dtype]
 
 
 def test_first_tokens_and_single_token_requests():

@@ -970,7 +970,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         for (int t = 0; t < n_mtiles; ++t) max_total = std::max(max_total, mix_band(h_pos[mtiles[2 * t]], mtiles[2 * t + 1], s.window, s.keep_first).total);
         const int ldu = (max_total + 63) / 64 * 64;
         const size_t per_row = (size_t)H * ldu;
-        const size_t budget_rows = std::max<size_t>(kAttnTile, ((size_t)24 << 20) / per_row);   // 96 MiB of scores: most of them stay in L2 between the passes, and a launch fills the GPU
+        const size_t budget_rows = std::min<size_t>(32768, std::max<size_t>(kAttnTile, ((size_t)24 << 20) / per_row));   // 96 MiB of scores: most of them stay in L2 between the passes, and a launch fills the GPU
         for (int t0 = 0; t0 < n_mtiles;) {
             int t1 = t0, rows = 0;
             bool big = false, small = false;
