@@ -54,15 +54,15 @@ def tudasun_config_for(size: str) -> dict:
 
 
 def gulazen_config_for(size: str) -> dict:
-    """Seven attention layers behind a four-tap convolution: the size's heads and window with 4 kept first keys, capped and mixed
+    """Seven attention layers behind a three-tap convolution: the size's heads and window with 8 kept first keys, capped and mixed
     scores; dense xIELU feed-forwards in layers 0, 2, 4, 6 and routed experts (8 of a quarter of the dense inner size, 2 chosen by
     logits, a shared expert of half the dense size) in layers 1, 3, 5."""
     z = SIZES[size]
-    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": z["window"], "keep_first": 4},
-             "scale": 1.0 / math.sqrt(z["dim"]), "softcap": 50.0}
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": z["window"], "keep_first": 8},
+             "scale": 1.0 / math.sqrt(z["dim"]), "softcap": 30.0}
     dense = {"kind": "dense", "ff": z["ff"]}
     moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "router": {"experts": 8, "top": 2}, "shared": {"ff": z["ff"] // 2}}
-    return {"architecture": "Gulazen", "canon": {"taps": 4}, "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(7)],
+    return {"architecture": "Gulazen", "canon": {"taps": 3}, "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(7)],
             "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
 
 
