@@ -987,8 +987,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             const int nt_b = t1 - t0, d4 = (s.dim + 3) / 4 * 4, dv4 = (s.vdim + 3) / 4 * 4;
             if (big) {
                 // bf16 mode: split-half tensor-core products (fp32-accurate); fp32 mode keeps true fp32 arithmetic
-                if (bf && g_use_tc && s.dim % 16 == 0) TRY(launch_dep(mix_scores_tiles_kernel<true>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 8) * sizeof(float), q, sm, s, a, kp));
-                else TRY(launch_dep(mix_scores_tiles_kernel<false>, dim3(ldu / 64, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 8) * sizeof(float), q, sm, s, a, kp));
+                if (bf && g_use_tc && s.dim % 16 == 0) TRY(launch_dep(mix_scores_tiles_kernel<true>, dim3((ldu / 64 + 2) / 3, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 8) * sizeof(float), q, sm, s, a, kp));
+                else TRY(launch_dep(mix_scores_tiles_kernel<false>, dim3((ldu / 64 + 2) / 3, nt_b, H), dim3(256), (size_t)2 * 64 * (d4 + 8) * sizeof(float), q, sm, s, a, kp));
                 LAUNCHED();
             }
             if (small) {

@@ -13,7 +13,8 @@
 //   * a causal depth-wise short convolution over time in front of a mixer, y_t = x_t + sum_j w[:, j] x_(t - taps + 1 + j), whose
 //     last taps - 1 inputs are sequence state (short_conv_kernel, short_conv_save_kernel).
 //
-// Everything here is fp32 in both compute modes: scores, cap, mixing, softmax and the weighted sum of values.
+// Everything here is fp32 in both compute modes: scores, cap, mixing, softmax and the weighted sum of values (in bf16 mode the two
+// products of prompt tiles run on the tensor cores over fp16 hi / lo halves of their fp32 operands, which keeps fp32 accuracy).
 #pragma once
 #include "prefill.cuh"
 #include "seq_kernels.cuh"
@@ -130,7 +131,7 @@ __device__ __forceinline__ float mix_cap(float v, const AttnShape& s) {
 }
 __device__ __forceinline__ size_t mix_token(const int* table, int j) { return (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens; }
 
-// pass 1, prompt portions: grid (band tiles of 64 keys, tiles of the batch, heads).  TC (bf16 mode, head size in whole 16-element
+// pass 1, prompt portions: grid (groups of the band's 64-key tiles, tiles of the batch, heads).  TC (bf16 mode, head size in whole 16-element
 // steps): the product runs on the warp-level tensor cores at fp32 accuracy, the split-half scheme of window_attention_h3_kernel --
 // every fp32 operand is split into two fp16 halves (x = hi + lo) as it is staged, and lo*hi + hi*lo + hi*hi is accumulated in fp32
 // by mma.sync m16n8k16; a warp owns 16 rows x 32 keys.  Otherwise true fp32 multiply-adds, 4 rows x 4 keys a thread.
@@ -143,8 +144,7 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
     if (n < a.small) return;
     const int p0 = m.row_pos[row0];
     const MixBand b = mix_band(p0, n, s.window, s.keep_first);
-    const int u0 = blockIdx.x * 64;
-    if (u0 >= b.total) return;
+    if ((int)blockIdx.x * 64 >= b.total) return;
     const int d = s.dim, d4 = (d + 3) / 4 * 4, ldq = d4 + 4, h = blockIdx.z, g = h / (s.heads / s.kv_heads);
     float* Qs = mixsm;
     float* Ks = Qs + 64 * ldq;
@@ -164,94 +164,99 @@ __global__ void __launch_bounds__(256) mix_scores_tiles_kernel(const float* qkv,
     const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
     const size_t kstride = (size_t)s.kv_heads * d;
     const bool vec = (d % 4 == 0) && (s.ld % 4 == 0);
+    // the query tile is staged (and split) once; the block then walks the band's key tiles blockIdx.x, blockIdx.x + gridDim.x, ...
     for (int i = tid; i < 64 * (d4 / 4); i += 256) {
         const int r = i / (d4 / 4), k4 = (i % (d4 / 4)) * 4;
-        float4 q = make_float4(0.f, 0.f, 0.f, 0.f), k = q;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < n) {
             const float* src = qkv + (size_t)(row0 + r) * s.ld + (size_t)h * d + k4;
             if (vec) q = *reinterpret_cast<const float4*>(src);
             else { q.x = src[0]; if (k4 + 1 < d) q.y = src[1]; if (k4 + 2 < d) q.z = src[2]; if (k4 + 3 < d) q.w = src[3]; }
         }
-        if (u0 + r < b.total) {
-            const float* src = k_pool + mix_token(table, b.key(u0 + r)) * kstride + (size_t)g * d + k4;
-            if (vec) k = *reinterpret_cast<const float4*>(src);
-            else { k.x = src[0]; if (k4 + 1 < d) k.y = src[1]; if (k4 + 2 < d) k.z = src[2]; if (k4 + 3 < d) k.w = src[3]; }
+        if constexpr (TC) store_split4(q, Qh + r * LD + k4, Ql + r * LD + k4);
+        else *reinterpret_cast<float4*>(&Qs[r * ldq + k4]) = q;
+    }
+    for (int u0 = blockIdx.x * 64; u0 < b.total; u0 += gridDim.x * 64) {
+        __syncthreads();   // (the key tile of the round before has been read)
+        for (int i = tid; i < 64 * (d4 / 4); i += 256) {
+            const int r = i / (d4 / 4), k4 = (i % (d4 / 4)) * 4;
+            float4 k = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (u0 + r < b.total) {
+                const float* src = k_pool + mix_token(table, b.key(u0 + r)) * kstride + (size_t)g * d + k4;
+                if (vec) k = *reinterpret_cast<const float4*>(src);
+                else { k.x = src[0]; if (k4 + 1 < d) k.y = src[1]; if (k4 + 2 < d) k.z = src[2]; if (k4 + 3 < d) k.w = src[3]; }
+            }
+            if constexpr (TC) store_split4(k, Kh + r * LD + k4, Kl + r * LD + k4);
+            else *reinterpret_cast<float4*>(&Ks[r * ldq + k4]) = k;
         }
+        __syncthreads();
         if constexpr (TC) {
-            store_split4(q, Qh + r * LD + k4, Ql + r * LD + k4);
-            store_split4(k, Kh + r * LD + k4, Kl + r * LD + k4);
-        } else {
-            *reinterpret_cast<float4*>(&Qs[r * ldq + k4]) = q;
-            *reinterpret_cast<float4*>(&Ks[r * ldq + k4]) = k;
-        }
-    }
-    __syncthreads();
-    if constexpr (TC) {
-        const int warp = tid >> 5, lane = tid & 31, gg = lane >> 2, t = lane & 3, rg = warp & 3, kh = warp >> 2;
-        float c[4][4];
+            const int warp = tid >> 5, lane = tid & 31, gg = lane >> 2, t = lane & 3, rg = warp & 3, kh = warp >> 2;
+            float c[4][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
-        const uint32_t* qh_row = reinterpret_cast<const uint32_t*>(Qh + (16 * rg + gg) * LD) + t;
-        const uint32_t* ql_row = reinterpret_cast<const uint32_t*>(Ql + (16 * rg + gg) * LD) + t;
-        const int lm = lane >> 3, lr = lane & 7;
-        const uint32_t k_ld = (uint32_t)(((lr + 8 * (lm >> 1)) * LD + 8 * (lm & 1)) * 2);
-        const uint32_t kh_s = smem_u32(Kh), kl_s = smem_u32(Kl);
-        for (int ks = 0; ks < d / 16; ++ks) {
-            const uint32_t ah[4] = {qh_row[8 * ks], qh_row[8 * ks + 4 * LD], qh_row[8 * ks + 4], qh_row[8 * ks + 4 * LD + 4]};
-            const uint32_t al[4] = {ql_row[8 * ks], ql_row[8 * ks + 4 * LD], ql_row[8 * ks + 4], ql_row[8 * ks + 4 * LD + 4]};
+            for (int i = 0; i < 4; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+            const uint32_t* qh_row = reinterpret_cast<const uint32_t*>(Qh + (16 * rg + gg) * LD) + t;
+            const uint32_t* ql_row = reinterpret_cast<const uint32_t*>(Ql + (16 * rg + gg) * LD) + t;
+            const int lm = lane >> 3, lr = lane & 7;
+            const uint32_t k_ld = (uint32_t)(((lr + 8 * (lm >> 1)) * LD + 8 * (lm & 1)) * 2);
+            const uint32_t kh_s = smem_u32(Kh), kl_s = smem_u32(Kl);
+            for (int ks = 0; ks < d / 16; ++ks) {
+                const uint32_t ah[4] = {qh_row[8 * ks], qh_row[8 * ks + 4 * LD], qh_row[8 * ks + 4], qh_row[8 * ks + 4 * LD + 4]};
+                const uint32_t al[4] = {ql_row[8 * ks], ql_row[8 * ks + 4 * LD], ql_row[8 * ks + 4], ql_row[8 * ks + 4 * LD + 4]};
 #pragma unroll
-            for (int jp = 0; jp < 2; ++jp) {
-                uint32_t bh[4], bl[4];
-                const uint32_t off = (uint32_t)(((32 * kh + 16 * jp) * LD + 16 * ks) * 2) + k_ld;
-                ldsm_x4(bh, kh_s + off);
-                ldsm_x4(bl, kl_s + off);
-                mma_f16(c[2 * jp], al, bh[0], bh[1]);
-                mma_f16(c[2 * jp + 1], al, bh[2], bh[3]);
-                mma_f16(c[2 * jp], ah, bl[0], bl[1]);
-                mma_f16(c[2 * jp + 1], ah, bl[2], bl[3]);
-                mma_f16(c[2 * jp], ah, bh[0], bh[1]);
-                mma_f16(c[2 * jp + 1], ah, bh[2], bh[3]);
+                for (int jp = 0; jp < 2; ++jp) {
+                    uint32_t bh[4], bl[4];
+                    const uint32_t off = (uint32_t)(((32 * kh + 16 * jp) * LD + 16 * ks) * 2) + k_ld;
+                    ldsm_x4(bh, kh_s + off);
+                    ldsm_x4(bl, kl_s + off);
+                    mma_f16(c[2 * jp], al, bh[0], bh[1]);
+                    mma_f16(c[2 * jp + 1], al, bh[2], bh[3]);
+                    mma_f16(c[2 * jp], ah, bl[0], bl[1]);
+                    mma_f16(c[2 * jp + 1], ah, bl[2], bl[3]);
+                    mma_f16(c[2 * jp], ah, bh[0], bh[1]);
+                    mma_f16(c[2 * jp + 1], ah, bh[2], bh[3]);
+                }
             }
-        }
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int r = 16 * rg + gg + 8 * half;
-            if (r >= n) continue;
-            float* dst = a.S + ((size_t)(row0 + r - a.row_base) * s.heads + h) * a.ldu + u0;
+            for (int half = 0; half < 2; ++half) {
+                const int r = 16 * rg + gg + 8 * half;
+                if (r >= n) continue;
+                float* dst = a.S + ((size_t)(row0 + r - a.row_base) * s.heads + h) * a.ldu + u0;
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int key = 32 * kh + 8 * nt + 2 * t;
-                if (u0 + key < b.total) dst[key] = mix_cap(c[nt][2 * half], s);
-                if (u0 + key + 1 < b.total) dst[key + 1] = mix_cap(c[nt][2 * half + 1], s);
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int key = 32 * kh + 8 * nt + 2 * t;
+                    if (u0 + key < b.total) dst[key] = mix_cap(c[nt][2 * half], s);
+                    if (u0 + key + 1 < b.total) dst[key + 1] = mix_cap(c[nt][2 * half + 1], s);
+                }
             }
+            continue;
         }
-        return;
-    }
-    float sc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
-    for (int k = 0; k < d4; k += 4) {
-        float4 qa[4], kk[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) qa[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ldq + k]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) kk[j] = *reinterpret_cast<const float4*>(&Ks[(tx + 16 * j) * ldq + k]);
+        float sc[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
+            for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+        for (int k = 0; k < d4; k += 4) {
+            float4 qa[4], kk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qa[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ldq + k]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) kk[j] = *reinterpret_cast<const float4*>(&Ks[(tx + 16 * j) * ldq + k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    sc[i][j] = fmaf(qa[i].x, kk[j].x, fmaf(qa[i].y, kk[j].y, fmaf(qa[i].z, kk[j].z, fmaf(qa[i].w, kk[j].w, sc[i][j]))));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = ty + 16 * i;
+            if (r >= n) continue;
+            float* dst = a.S + ((size_t)(row0 + r - a.row_base) * s.heads + h) * a.ldu + u0;
+#pragma unroll
             for (int j = 0; j < 4; ++j)
-                sc[i][j] = fmaf(qa[i].x, kk[j].x, fmaf(qa[i].y, kk[j].y, fmaf(qa[i].z, kk[j].z, fmaf(qa[i].w, kk[j].w, sc[i][j]))));
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = ty + 16 * i;
-        if (r >= n) continue;
-        float* dst = a.S + ((size_t)(row0 + r - a.row_base) * s.heads + h) * a.ldu + u0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (u0 + tx + 16 * j < b.total) dst[tx + 16 * j] = mix_cap(sc[i][j], s);
+                if (u0 + tx + 16 * j < b.total) dst[tx + 16 * j] = mix_cap(sc[i][j], s);
+        }
     }
 }
 
