@@ -296,16 +296,18 @@ def test_convolution_state_crosses_every_cut():
     m.free()
 
 
+@pytest.mark.parametrize("heads,window,n", [(20, 900, 1000), (16, 1200, 1260)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_window_many_heads(dtype):
-    """20 heads over a window of 900 keys: a row's scores of all heads (20 x 960 numbers) no longer fit the shared memory of the
-    mixing pass, which then keeps them in the score scratch between its two sweeps; prompt tiles and decoded rows."""
-    cfg = make_config([layer(heads=20, kv_heads=4, dim=16, vdim=8, window=900, keep=3, mlp=dense(32))], width=40)
+def test_long_window_many_heads(dtype, heads, window, n):
+    """A row's scores of all heads over a long window: 20 heads x 960 keys take the mixing pass that works out of shared memory
+    (more than 16 heads); 16 heads x 1280 keys no longer fit beside the register form, which then keeps them in the score scratch
+    between its two sweeps.  Prompt tiles and decoded rows."""
+    cfg = make_config([layer(heads=heads, kv_heads=4, dim=16, vdim=8, window=window, keep=3, mlp=dense(32))], width=40)
     W = random_weights(cfg, seed=23)
-    toks = tokens(1000, cfg["vocab"], 9)
+    toks = tokens(n, cfg["vocab"], 9)
     want, _ = plain.run(cfg, W, toks)
-    m = build_engine(cfg, W, dtype, max_tokens=1024)
-    got = run_schedule(m, {"a": toks}, [[("a", 700)], [("a", 3)], [("a", 290)]] + [[("a", 1)]] * 7)["a"]
+    m = build_engine(cfg, W, dtype, max_tokens=(n + 63) // 64 * 64)
+    got = run_schedule(m, {"a": toks}, [[("a", n - 300)], [("a", 3)], [("a", 290)]] + [[("a", 1)]] * 7)["a"]
     m.free()
     assert rel_err(got, want) < TOL[dtype]
 

@@ -1000,6 +1000,12 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             const size_t row_bytes = per_row * sizeof(float);
             const int in_smem = row_bytes <= 72 * 1024 ? 1 : 0;
             const size_t sm2 = in_smem ? row_bytes : 0;
+            // more than 16 heads: the form that mixes out of shared memory, when a row's scores of all heads fit there
+            if (L.mix_HP >= 32 && mix_softmax_wide_smem_bytes(H, ldu) <= g_smem_optin) {
+                if (H <= 32) TRY(launch_dep(mix_softmax_wide_kernel<8>, g2, dim3(kMixWideThreads), mix_softmax_wide_smem_bytes(H, ldu), sm, s, a));
+                else TRY(launch_dep(mix_softmax_wide_kernel<16>, g2, dim3(kMixWideThreads), mix_softmax_wide_smem_bytes(H, ldu), sm, s, a));
+                LAUNCHED();
+            } else {
             // (few rows: 512 threads a row have more of its loads in flight; many rows fill the GPU better with 256)
             if (L.mix_HP == 8 && !big) TRY(launch_dep(mix_softmax_kernel<8, 512>, g2, dim3(512), sm2, sm, s, a, in_smem));
             else if (L.mix_HP == 16 && !big) TRY(launch_dep(mix_softmax_kernel<16, 512>, g2, dim3(512), sm2, sm, s, a, in_smem));
@@ -1008,6 +1014,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             else if (L.mix_HP == 32) TRY(launch_dep(mix_softmax_kernel<32, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
             else TRY(launch_dep(mix_softmax_kernel<64, 256>, g2, dim3(256), sm2, sm, s, a, in_smem));
             LAUNCHED();
+            }
             if (big) {
                 if (bf && g_use_tc) TRY(launch_dep(mix_values_tiles_kernel<true>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)4 * 64 * 72 * sizeof(__half), sm, s, a, vp, out));
                 else TRY(launch_dep(mix_values_tiles_kernel<false>, dim3(nt_b, H, (dv4 + 63) / 64), dim3(256), (size_t)64 * (68 + 64) * sizeof(float), sm, s, a, vp, out));
@@ -1391,6 +1398,8 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(mix_scores_rows_kernel<kAttnMaxPerLane>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(mix_softmax_kernel<8, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     CK(cudaFuncSetAttribute(mix_softmax_kernel<16, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    CK(cudaFuncSetAttribute(mix_softmax_wide_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(mix_softmax_wide_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(mix_softmax_kernel<8, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     CK(cudaFuncSetAttribute(mix_softmax_kernel<16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     CK(cudaFuncSetAttribute(mix_softmax_kernel<32, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));

@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(256) mix_scores_rows_kernel(const float* qkv, 
 // pass 2: grid (64, tiles of the batch); block (r, tile) owns row r of the tile and all heads: every key's H scores are mixed in
 // registers and masked, then every head's weights exp(s - max) replace its scores and 1 / (their sum + exp(sink - max)) is kept
 template <int HP, int NT>   // NT threads: 512 where the heads' registers allow it (more of a row's loads in flight), else 256
-__global__ void __launch_bounds__(NT) mix_softmax_kernel(StepMeta m, AttnShape s, MixArgs a, int in_smem) {
+__global__ void __launch_bounds__(NT, (HP <= 16 && NT == 256) ? 3 : 1) mix_softmax_kernel(StepMeta m, AttnShape s, MixArgs a, int in_smem) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     extern __shared__ __align__(16) float mixsm[];   // in_smem: [H][ldu] the row's mixed scores between the two sweeps
@@ -396,11 +396,103 @@ __global__ void __launch_bounds__(NT) mix_softmax_kernel(StepMeta m, AttnShape s
     }
 }
 
+// pass 2 for many heads (more than 16: the register form above would hold 32 or 64 scores, maxima and sums a thread): the row's scores
+// of all heads are copied to shared memory [H][ldu] first; then four lanes share a group of FOUR neighbouring keys, each mixing a
+// quarter of the heads (QW = 8 or 16 of them) from the H scores of those keys in shared memory (T transposed, so that a lane's heads
+// are contiguous: one score vector and QW / 4 vectors of T a step for 4 QW multiply-adds) and writing them back in place once all
+// four have read (they sit in one warp); then one warp per head takes the maximum, writes exp(s - max) to the scratch and keeps
+// 1 / (sum + exp(sink - max)).  grid (64, tiles of the batch), 512 threads.
+constexpr int kMixWideThreads = 512;
+__host__ __device__ inline size_t mix_softmax_wide_smem_bytes(int H, int ldu) { return ((size_t)H * ldu + (size_t)H * 64) * sizeof(float); }
+template <int QW>   // heads a lane mixes: up to 4 x QW heads
+__global__ void __launch_bounds__(kMixWideThreads) mix_softmax_wide_kernel(StepMeta m, AttnShape s, MixArgs a) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    extern __shared__ __align__(16) float mixsm[];
+    const int tile = a.tile0 + blockIdx.y, row0 = a.tiles[2 * tile], n = a.tiles[2 * tile + 1], r = blockIdx.x;
+    if (r >= n) return;
+    const int H = s.heads, HQ = (H + 3) / 4, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, ldu = a.ldu;
+    constexpr int NW = kMixWideThreads / 32, LT = 4 * QW;
+    float* R = mixsm;                 // [H][ldu]
+    float* Tt = R + (size_t)H * ldu;  // [H (g)][LT]: Tt[g][q * QW + k] = T[q * HQ + k][g] (identity without a mixing matrix)
+    const int p0 = m.row_pos[row0], pos = p0 + r;
+    const MixBand b = mix_band(p0, n, s.window, s.keep_first);
+    float* base = a.S + (size_t)(row0 + r - a.row_base) * H * ldu;
+    for (int i = tid; i < H * LT; i += kMixWideThreads) {
+        const int g = i / LT, q = (i % LT) / QW, k = i % QW, h = q * HQ + k;
+        Tt[i] = (k < HQ && h < H) ? (s.talk ? s.talk[h * H + g] : (h == g ? 1.f : 0.f)) : 0.f;
+    }
+    for (int i = tid; i < H * (ldu / 4); i += kMixWideThreads) {   // (whole vectors of the scratch: what lies beyond the band is never used)
+        const int h = i / (ldu / 4), u4 = (i % (ldu / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (u4 < b.total) v = *reinterpret_cast<const float4*>(base + (size_t)h * ldu + u4);
+        *reinterpret_cast<float4*>(R + (size_t)h * ldu + u4) = v;
+    }
+    __syncthreads();
+    const int q = lane >> 3;   // this lane's quarter of the heads: q * HQ .. q * HQ + HQ - 1
+    for (int u = warp * 32 + 4 * (lane & 7); u < (b.total + 31) / 32 * 32; u += NW * 32) {   // (whole groups of 32 keys: a warp stays together)
+        const bool in = u < b.total;
+        float acc[4][QW];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int k = 0; k < QW; ++k) acc[c][k] = 0.f;
+        if (in)
+            for (int g = 0; g < H; ++g) {
+                const float4 sv = *reinterpret_cast<const float4*>(R + (size_t)g * ldu + u);
+                const float4* tr = reinterpret_cast<const float4*>(Tt + g * LT + q * QW);
+#pragma unroll
+                for (int k4 = 0; k4 < QW / 4; ++k4) {
+                    const float4 tv = tr[k4];
+                    const float t4[4] = {tv.x, tv.y, tv.z, tv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc[0][4 * k4 + e] = fmaf(t4[e], sv.x, acc[0][4 * k4 + e]);
+                        acc[1][4 * k4 + e] = fmaf(t4[e], sv.y, acc[1][4 * k4 + e]);
+                        acc[2][4 * k4 + e] = fmaf(t4[e], sv.z, acc[2][4 * k4 + e]);
+                        acc[3][4 * k4 + e] = fmaf(t4[e], sv.w, acc[3][4 * k4 + e]);
+                    }
+                }
+            }
+        __syncwarp();   // the four lanes of a key group have read its scores
+        if (in) {
+            bool seen[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int j = b.key(min(u + c, b.total - 1));
+                seen[c] = u + c < b.total && j <= pos && (s.window <= 0 || pos - j < s.window || j < s.keep_first);
+            }
+#pragma unroll
+            for (int k = 0; k < QW; ++k)
+                if (k < HQ && q * HQ + k < H)
+                    *reinterpret_cast<float4*>(R + (size_t)(q * HQ + k) * ldu + u) =
+                        make_float4(seen[0] ? acc[0][k] : -INFINITY, seen[1] ? acc[1][k] : -INFINITY, seen[2] ? acc[2][k] : -INFINITY, seen[3] ? acc[3][k] : -INFINITY);
+        }
+    }
+    __syncthreads();
+    for (int h = warp; h < H; h += NW) {
+        const float* rr = R + (size_t)h * ldu;
+        float mx = -INFINITY;
+        for (int u = lane; u < b.total; u += 32) mx = fmaxf(mx, rr[u]);
+        mx = warp_max(mx);
+        if (s.sink) mx = fmaxf(mx, s.sink[h]);
+        float sum = 0.f;
+        for (int u = lane; u < b.total; u += 32) {
+            const float v = rr[u];
+            const float e = v == -INFINITY ? 0.f : expf(v - mx);
+            base[(size_t)h * ldu + u] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) a.inv_den[(size_t)(row0 + r - a.row_base) * H + h] = 1.f / (sum + (s.sink ? expf(s.sink[h] - mx) : 0.f));
+    }
+}
+
 // pass 3, prompt portions: grid (tiles of the batch, heads, groups of 64 value columns); O[64 rows][64 columns] = sum over the band's
 // 64-key tiles of P V, 4 rows x 4 columns a thread -- or, TC (bf16 mode), split-half tensor-core products as in pass 1 (the value tile
 // is read through transposing matrix loads), a warp owning 16 rows x 32 columns
 template <bool TC>
-__global__ void __launch_bounds__(256) mix_values_tiles_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
+__global__ void __launch_bounds__(256, 3) mix_values_tiles_kernel(StepMeta m, AttnShape s, MixArgs a, const float* v_pool, float* out) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     extern __shared__ __align__(16) float mixsm[];
