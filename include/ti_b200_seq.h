@@ -51,9 +51,18 @@ enum {
 };
 enum {
     TI_SEQ_NORMS_AROUND = 0, /* a norm in front of every sublayer ("norm1", "norm2") and one behind it ("norm1b", "norm2b") */
-    TI_SEQ_NORMS_BEHIND = 1  /* the sublayers read the residual stream itself; one norm behind each ("norm1", "norm2") */
+    TI_SEQ_NORMS_BEHIND = 1, /* the sublayers read the residual stream itself; one norm behind each ("norm1", "norm2") */
+    TI_SEQ_NORMS_FRONT = 2   /* one norm in front of every sublayer ("norm1", "norm2"), none behind it */
 };
-enum { TI_SEQ_NORM_SCALAR = 0 /* one gain for all coordinates */, TI_SEQ_NORM_ONE_PLUS = 1 /* per-coordinate gain stored as w, applied as 1 + w */ };
+enum {
+    TI_SEQ_NORM_SCALAR = 0 /* one gain for all coordinates */, TI_SEQ_NORM_ONE_PLUS = 1 /* per-coordinate gain stored as w, applied as 1 + w */,
+    TI_SEQ_NORM_VECTOR = 2 /* per-coordinate gain applied as it is stored */
+};
+enum {
+    TI_SEQ_SINK_NONE = 0,
+    TI_SEQ_SINK_LEARNED = 1, /* the softmax denominator has one more term exp(sink[head]) ("mix.sink") without key or value */
+    TI_SEQ_SINK_ZERO = 2     /* the same term with a fixed score of 0: p_j = exp(s_j) / (1 + sum exp(s)); no tensor */
+};
 enum { TI_SEQ_BF16 = 0, TI_SEQ_F32 = 1 };   /* compute mode of a model, and element type of a tensor handed to set_tensor */
 
 typedef struct ti_seq_layer_desc {
@@ -76,7 +85,7 @@ typedef struct ti_seq_layer_desc {
     /* -- latent attention: dim = unrotated query/key size, rot_dims = rotated part (one key part shared by the heads), vdim -- */
     int32_t kv_rank;         /* size of the cached low-rank vector */
     int32_t kv_from;         /* -1: the layer projects and caches its own; j: it reads layer j's cache (j before this layer) */
-    int32_t sink;            /* 1: the softmax denominator has one more term exp(sink[head]) without key or value */
+    int32_t sink;            /* TI_SEQ_SINK_* */
     /* -- feed-forward -- */
     int32_t ff_kind;         /* TI_SEQ_FF_*; `ff` is the inner size of the dense forms and of one routed expert */
     int32_t experts;         /* routed experts with weights */
@@ -98,6 +107,17 @@ typedef struct ti_seq_layer_desc {
     int32_t conv_taps;       /* >= 1: the mixer reads h + conv(h), a causal depth-wise convolution over the last `conv_taps` inputs of the
                                 sequence ("canon1" [width][taps], zeros before position 0); the last taps - 1 inputs are sequence state */
     int32_t layer_scale;     /* 1: each sublayer's normed result is multiplied coordinate by coordinate by "ls1" / "ls2" before the residual sum */
+    int32_t conv_ff;         /* 1 (with conv_taps >= 1): the feed-forward reads through a convolution of its own too ("canon2") */
+    /* -- rotation, attention and latent attention -- */
+    int32_t rot_half;        /* 1: rotated coordinate i pairs with i + rot_dims / 2 instead of (2i, 2i + 1) */
+    float rot_linear;        /* > 0: every frequency is divided by this number (independent of the wavelength) */
+    /* -- attention -- */
+    int32_t proj_bias;       /* 1: the q, k, v and output projections add biases ("mix.q.b", "mix.k.b", "mix.v.b", "mix.o.b") */
+    int32_t v_norm;          /* 1: every value head is divided by its RMS (no weight) before it is cached */
+    int32_t head_temp;       /* 1: the scaled score of query head h is multiplied by "mix.temp"[h] */
+    /* -- latent attention (`window` and `out_gate` above apply to it as well: "mix.g" [heads][width]) -- */
+    int32_t q_rank;          /* > 0: queries through a low-rank vector: q = Uq norm(Dq h) ("mix.dq" [q_rank][width], "mix.dq.norm",
+                                "mix.uq" [heads * (dim + rot_dims)][q_rank]); 0: "mix.q" */
 } ti_seq_layer_desc;
 
 typedef struct ti_seq_model_desc {
@@ -117,6 +137,11 @@ typedef struct ti_seq_model_desc {
     float pos_base;          /* > 0: a sinusoidal position vector is added to the embedding: entry 2i = sin(p * base^(-2i/width)),
                                 entry 2i + 1 = cos of the same angle */
     int32_t tied_head;       /* 1: the logits are products with the embedding table (no "head" tensor) */
+    int32_t loop_plain;      /* 1: the passes of the looped block follow one another directly (no "loop.in" projection) */
+    int32_t streams;         /* >= 1: hyper-connections.  The residual is `streams` copies X_s of the embedding output; sublayer q of a layer
+                                reads u = sum_s hcq.in[s] X_s and, with its result y, all copies are rewritten at once from the old ones:
+                                X_t <- sum_s hcq.mix[s][t] X_s + hcq.out[t] y ("l<i>.hc1.*" mixer, "l<i>.hc2.*" feed-forward); the model's
+                                output is sum_s X_s.  Needs TI_SEQ_NORMS_FRONT.  0: one residual stream, x <- x + y */
 } ti_seq_model_desc;
 
 int ti_seq_init(int device);
@@ -125,7 +150,7 @@ uint64_t ti_seq_launch_count(void);
 
 int ti_seq_model_new(const ti_seq_model_desc* desc, const ti_seq_layer_desc* layers, ti_seq_model_t* out);
 /* tensor names: "embed", "side.embed", "loop.in", "final.norm", "head", "l<i>.norm1|norm1b|norm2|norm2b", "l<i>.rg1|rg2[.b]",
- * "l<i>.ls1|ls2", "l<i>.canon1", "l<i>.mix.<x>", "l<i>.mlp.<x>", "l<i>.side.<x>";
+ * "l<i>.ls1|ls2", "l<i>.canon1|canon2", "l<i>.hc1|hc2.in|out|mix", "l<i>.mix.<x>", "l<i>.mlp.<x>", "l<i>.side.<x>";
  * `dtype` is the element type of `data` (TI_SEQ_BF16: raw bfloat16 bits, TI_SEQ_F32) */
 int ti_seq_model_set_tensor(ti_seq_model_t m, const char* name, int32_t dtype, const void* data, const int64_t* shape, int32_t ndim);
 /* uniform(-amp, amp) + offset generated on the device from (seed, element index): benchmark-size models */

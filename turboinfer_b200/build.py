@@ -43,7 +43,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 # quantized-decoder library to compile.
 SEQ_LIB = os.path.join(HERE, "libturboinfer_b200_seq.so")
 SEQ_SOURCES = ["seq_engine.cu"]
-SEQ_HEADERS = ["seq_kernels.cuh", "seq_headmix.cuh", "seq_gemm_tc.cuh", "seq_attn_tc.cuh", "seq_recurrent.cuh", "seq_latent.cuh", "seq_experts.cuh", "prefill.cuh", "gemm_tc.cuh", "sampling.cuh", "kernels.cuh", "gemv.cuh", "qlayout.cuh", "ptx.cuh"]
+SEQ_HEADERS = ["seq_kernels.cuh", "seq_headmix.cuh", "seq_hyper.cuh", "seq_gemm_tc.cuh", "seq_attn_tc.cuh", "seq_recurrent.cuh", "seq_latent.cuh", "seq_experts.cuh", "prefill.cuh", "gemm_tc.cuh", "sampling.cuh", "kernels.cuh", "gemv.cuh", "qlayout.cuh", "ptx.cuh"]
 
 
 def build_seq(force: bool = False) -> str:

@@ -3,7 +3,7 @@
 // halves, 22 mantissa bits, and hi*hi + hi*lo + lo*hi accumulated in fp32 by mma.sync m16n8k16), generalised to
 //   - ragged steps: a block owns up to 128 consecutive rows of ONE sequence (tiles[2 i] = first row, tiles[2 i + 1] = count),
 //   - grouped key/value heads, a sliding window (only the pages the tile's rows can see are visited),
-//   - the per-head sigmoid output gate.
+//   - the per-head sigmoid output gate and the sink term of the softmax denominator.
 // Scores, softmax and the running sums are fp32.  Head sizes 64 and 128 with dim == vdim; other shapes use the fp32 tiled kernel.
 // Also here: the split-key attention of decode rows (flash-decoding: key chunks in parallel, then a merge).
 #pragma once
@@ -161,10 +161,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) window_attention_h3_kernel(cons
             }
         }
     }
-    const size_t gate_off = (size_t)(s.heads + s.kv_heads) * DH + (size_t)s.kv_heads * DH + h;
     float i0 = 0.f, i1 = 0.f;
-    if (r0 < M) i0 = (s.out_gate ? 1.f / (1.f + expf(-qkvg[(size_t)(row0 + r0) * s.ld + gate_off])) : 1.f) / l0;
-    if (r1 < M) i1 = (s.out_gate ? 1.f / (1.f + expf(-qkvg[(size_t)(row0 + r1) * s.ld + gate_off])) : 1.f) / l1;
+    if (r0 < M) i0 = attn_gate(s, qkvg, row0 + r0, h) * attn_finish_factor(s, h, m0, l0);
+    if (r1 < M) i1 = attn_gate(s, qkvg, row0 + r1, h) * attn_finish_factor(s, h, m1, l1);
     const size_t opitch = (size_t)s.heads * DH;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -283,12 +282,7 @@ __global__ void attention_merge_kernel(const float* part, const float* qkvg, Ste
     const float Mx = warp_max(mz);
     const float fz = mz == -INFINITY ? 0.f : expf(mz - Mx);
     const float L = warp_sum(lz * fz);
-    float gate = 1.f;
-    if (s.out_gate) {
-        const float zg = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
-        gate = 1.f / (1.f + expf(-zg));
-    }
-    const float fin = attn_finish_factor(s, h, Mx, L) * gate;
+    const float fin = attn_finish_factor(s, h, Mx, L) * attn_gate(s, qkvg, t, h);
     // every split's factor in registers first, so that the loads of a coordinate's partials do not wait on one another
     constexpr int kMaxSplits = 32;   // (a lane holds a split's statistics)
     float fs[kMaxSplits];

@@ -23,6 +23,7 @@
 #include "seq_latent.cuh"
 #include "seq_experts.cuh"
 #include "seq_headmix.cuh"
+#include "seq_hyper.cuh"
 #include "sampling.cuh"
 
 using namespace tib;
@@ -200,6 +201,13 @@ struct LayerW {
     // activation numbers (xielu: softplus(act[0]), 1/2 + softplus(act[1])); the router's bias
     const float *qnorm = nullptr, *knorm = nullptr, *talk = nullptr, *canon = nullptr, *route_bias = nullptr;
     float act_a = 0.f, act_b = 0.f;
+    // attention with biased projections / a per-head score factor / a fixed sink; latent attention with low-rank queries; a second
+    // convolution in front of the feed-forward; hyper-connections (index 0: mixer, 1: feed-forward)
+    DevBuf<float> qkv_bias, sink_zero;         // biases of the fused [q | k | v] product side by side; zeros [heads]
+    const float *o_bias = nullptr, *temp = nullptr, *canon2 = nullptr, *dqnorm = nullptr;
+    const void* uq = nullptr;
+    int off_dq = -1, ld_front = 0;             // ld_front: row stride of the fused front product's output (>= n_front: room for q behind it)
+    const float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
     int mix_HP = 0;   // > 0: the layer's attention is the head-mixing one; register bound of its head count (8 / 16 / 32 / 64)
 };
 
@@ -211,6 +219,7 @@ struct Run {
     DevBuf<float> state, prev;             // wkv: [slots][H][d][d], [slots][D]; gla / hgrn2: state [slots][H][dk][dv]
     int kv_run = -1;                       // latent attention reading another layer's cache: the run that owns it
     DevBuf<float> conv_state;              // short convolution: [slots][taps - 1][D], the last inputs of every sequence
+    DevBuf<float> conv_state2;             // the same for the convolution in front of the feed-forward
 };
 
 struct SeqState {
@@ -230,6 +239,8 @@ struct Model {
     const void *embed = nullptr, *loop_in = nullptr, *head = nullptr, *side_embed = nullptr;
     const float* final_norm = nullptr;
     DevBuf<float> pos_freq;           // sinusoidal positions: [ceil(width / 2)] frequencies
+    int n_streams = 0;                // copies of the residual the step keeps (norms in front only: >= 1)
+    DevBuf<float> xs, ones;           // [rows][streams][D]; ones: in / mix / out of the one-stream residual x <- x + y
     int gvec = 0;                     // 1: the norms around the sublayers have one gain per coordinate
     // cache manager
     int num_pages = 0;
@@ -286,23 +297,39 @@ bool is_recurrent(int mixer) { return mixer == TI_SEQ_MIXER_WKV || mixer == TI_S
 
 int describe_tensors(Model& m) {
     const int64_t D = m.d.width, V = m.d.vocab;
-    const std::vector<int64_t> gain_shape = m.d.norm_kind == TI_SEQ_NORM_ONE_PLUS ? std::vector<int64_t>{D} : std::vector<int64_t>{};
+    if (m.d.norm_kind != TI_SEQ_NORM_SCALAR && m.d.norm_kind != TI_SEQ_NORM_ONE_PLUS && m.d.norm_kind != TI_SEQ_NORM_VECTOR) return fail("norm kind %d", m.d.norm_kind);
+    const std::vector<int64_t> gain_shape = m.d.norm_kind != TI_SEQ_NORM_SCALAR ? std::vector<int64_t>{D} : std::vector<int64_t>{};
+    const bool front = m.d.norm_place == TI_SEQ_NORMS_FRONT;
+    if (m.d.streams < 0 || m.d.streams > kMaxStreams) return fail("%d residual streams (at most %d)", m.d.streams, kMaxStreams);
+    if (m.d.streams > 0 && !front) return fail("hyper-connections are built for norms in front of the sublayers only");
     require(m, "embed", {V, D}, true);
     if (m.d.side_dim > 0) require(m, "side.embed", {V, (int64_t)m.d.side_dim * m.d.n_layers}, true);
-    if (m.d.loop_times > 0) require(m, "loop.in", {D, 2 * D}, true);
+    if (m.d.loop_times > 0 && !m.d.loop_plain) require(m, "loop.in", {D, 2 * D}, true);
     for (int i = 0; i < m.d.n_layers; ++i) {
         const ti_seq_layer_desc& L = m.layers[i].d;
         const std::string p = "l" + std::to_string(i) + ".";
         const bool behind = m.d.norm_place == TI_SEQ_NORMS_BEHIND;
         require(m, p + "norm1", gain_shape, false);
-        if (!behind) require(m, p + "norm1b", gain_shape, false);
+        if (!behind && !front) require(m, p + "norm1b", gain_shape, false);
+        if (front && (L.res_gate || L.layer_scale || (L.mixer != TI_SEQ_MIXER_ATTENTION && L.mixer != TI_SEQ_MIXER_LATENT) || (L.ff > 0 && L.ff_kind != TI_SEQ_FF_GLU)))
+            return fail("layer %d: norms in front of the sublayers only are built for attention / latent attention layers with a gated feed-forward, without residual gates and layer scale", i);
+        for (int q = 1; q <= (m.d.streams > 0 ? (L.ff > 0 ? 2 : 1) : 0); ++q) {
+            const std::string hc = p + "hc" + std::to_string(q) + ".";
+            require(m, hc + "in", {(int64_t)m.d.streams}, false);
+            require(m, hc + "out", {(int64_t)m.d.streams}, false);
+            require(m, hc + "mix", {(int64_t)m.d.streams, (int64_t)m.d.streams}, false);
+        }
         if (L.layer_scale) {
             require(m, p + "ls1", {D}, false);
             if (L.ff > 0) require(m, p + "ls2", {D}, false);
         }
-        if (L.conv_taps >= 1 && L.mixer != TI_SEQ_MIXER_ATTENTION) return fail("layer %d: the short convolution is built in front of attention mixers", i);
+        if (L.conv_taps >= 1 && L.mixer != TI_SEQ_MIXER_ATTENTION && L.mixer != TI_SEQ_MIXER_LATENT) return fail("layer %d: the short convolution is built in front of attention and latent attention mixers", i);
         if (L.conv_taps >= 1) require(m, p + "canon1", {D, (int64_t)L.conv_taps}, false);
         else if (L.conv_taps < 0) return fail("layer %d: %d convolution taps", i, L.conv_taps);
+        if (L.conv_ff && L.conv_taps < 1) return fail("layer %d: a convolution in front of the feed-forward without taps", i);
+        if (L.conv_ff && L.ff > 0) require(m, p + "canon2", {D, (int64_t)L.conv_taps}, false);
+        if (L.sink != TI_SEQ_SINK_NONE && L.sink != TI_SEQ_SINK_LEARNED && L.sink != TI_SEQ_SINK_ZERO) return fail("layer %d: sink kind %d", i, L.sink);
+        if (L.rot_linear < 0.f) return fail("layer %d: frequency divisor %g", i, L.rot_linear);
         if (behind && (L.res_gate || L.mixer != TI_SEQ_MIXER_ATTENTION)) return fail("layer %d: norms behind the sublayers only are built for attention layers without residual gates", i);
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             if (L.heads <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) return fail("layer %d: heads %d / kv_heads %d", i, L.heads, L.kv_heads);
@@ -320,7 +347,17 @@ int describe_tensors(Model& m) {
                 require(m, p + "mix.k.norm", {(int64_t)L.kv_heads * L.dim}, false);
             } else if (L.qk_norm != TI_SEQ_QK_NORM_NONE && L.qk_norm != TI_SEQ_QK_NORM_HEAD) return fail("layer %d: q / k norm kind %d", i, L.qk_norm);
             if (L.talk) require(m, p + "mix.talk", {(int64_t)L.heads, (int64_t)L.heads}, false);
-            if (L.sink) require(m, p + "mix.sink", {(int64_t)L.heads}, false);
+            if (L.sink == TI_SEQ_SINK_LEARNED) require(m, p + "mix.sink", {(int64_t)L.heads}, false);
+            if (L.proj_bias) {
+                require(m, p + "mix.q.b", {(int64_t)L.heads * L.dim}, false);
+                require(m, p + "mix.k.b", {(int64_t)L.kv_heads * L.dim}, false);
+                require(m, p + "mix.v.b", {(int64_t)L.kv_heads * L.vdim}, false);
+                require(m, p + "mix.o.b", {D}, false);
+                if (!front) return fail("layer %d: the output projection's bias is built with norms in front of the sublayers only", i);
+            }
+            if (L.head_temp) require(m, p + "mix.temp", {(int64_t)L.heads}, false);
+            if ((L.proj_bias || L.head_temp || L.v_norm || L.rot_half) && L.qk_norm == TI_SEQ_QK_NORM_WHOLE)
+                return fail("layer %d: biases, per-head score factors, value norms and half-split rotation are built without the whole-projection q / k norm", i);
             if (L.keep_first < 0 || L.softcap < 0.f) return fail("layer %d: keep_first %d softcap %g", i, L.keep_first, L.softcap);
             if (L.talk || L.softcap > 0.f || L.keep_first > 0) {   // the head-mixing kernel takes the layer
                 if (L.out_gate || L.qk_norm == TI_SEQ_QK_NORM_HEAD || L.rot_dims > 0) return fail("layer %d: capped / mixed scores and kept first keys are built without rotation, per-head norm and output gate", i);
@@ -368,14 +405,22 @@ int describe_tensors(Model& m) {
                 if (S.mixer != TI_SEQ_MIXER_LATENT || S.kv_from >= 0 || S.kv_rank != L.kv_rank || S.rot_dims != L.rot_dims || S.rot_base != L.rot_base)
                     return fail("layer %d: layer %d has no cache of its own with the same rank, rotated size and rotation", i, L.kv_from);
             }
-            require(m, p + "mix.q", {(int64_t)L.heads * (L.dim + L.rot_dims), D}, true);
+            if (L.q_rank > 0) {
+                require(m, p + "mix.dq", {(int64_t)L.q_rank, D}, true);
+                require(m, p + "mix.dq.norm", {(int64_t)L.q_rank}, false);
+                require(m, p + "mix.uq", {(int64_t)L.heads * (L.dim + L.rot_dims), (int64_t)L.q_rank}, true);
+            } else if (L.q_rank == 0) {
+                require(m, p + "mix.q", {(int64_t)L.heads * (L.dim + L.rot_dims), D}, true);
+            } else return fail("layer %d: query rank %d", i, L.q_rank);
+            if (L.window < 0) return fail("layer %d: window %d", i, L.window);
+            if (L.out_gate) require(m, p + "mix.g", {(int64_t)L.heads, D}, true);
             if (L.kv_from < 0) {
                 require(m, p + "mix.dkv", {(int64_t)L.kv_rank + L.rot_dims, D}, true);
                 require(m, p + "mix.dkv.norm", {(int64_t)L.kv_rank}, false);
             }
             require(m, p + "mix.uk", {(int64_t)L.heads * L.dim, (int64_t)L.kv_rank}, true);
             require(m, p + "mix.uv", {(int64_t)L.heads * L.vdim, (int64_t)L.kv_rank}, true);
-            if (L.sink) require(m, p + "mix.sink", {(int64_t)L.heads}, false);
+            if (L.sink == TI_SEQ_SINK_LEARNED) require(m, p + "mix.sink", {(int64_t)L.heads}, false);
             require(m, p + "mix.o", {D, (int64_t)L.heads * L.vdim}, true);
         } else {
             return fail("layer %d: unknown mixer %d", i, L.mixer);
@@ -386,7 +431,7 @@ int describe_tensors(Model& m) {
         }
         if (L.ff > 0) {
             require(m, p + "norm2", gain_shape, false);
-            if (!behind) require(m, p + "norm2b", gain_shape, false);
+            if (!behind && !front) require(m, p + "norm2b", gain_shape, false);
             if (behind && L.ff_kind != TI_SEQ_FF_DENSE && L.ff_kind != TI_SEQ_FF_EXPERTS) return fail("layer %d: norms behind the sublayers only are built for the dense and the routed feed-forward", i);
             if (L.ff_kind == TI_SEQ_FF_DENSE) {
                 if (L.ff_act != TI_SEQ_ACT_XIELU && L.ff_act != TI_SEQ_ACT_RELU && L.ff_act != TI_SEQ_ACT_SILU && L.ff_act != TI_SEQ_ACT_GELU_TANH)
@@ -441,7 +486,8 @@ int describe_tensors(Model& m) {
     }
     require(m, "final.norm", gain_shape, false);
     if (!m.d.tied_head) require(m, "head", {V, D}, true);
-    if (m.d.norm_place != TI_SEQ_NORMS_AROUND && m.d.norm_place != TI_SEQ_NORMS_BEHIND) return fail("norm placement %d", m.d.norm_place);
+    if (m.d.norm_place != TI_SEQ_NORMS_AROUND && m.d.norm_place != TI_SEQ_NORMS_BEHIND && !front) return fail("norm placement %d", m.d.norm_place);
+    if (front && (m.d.side_dim > 0 || (m.d.loop_times > 0 && !m.d.loop_plain))) return fail("norms in front of the sublayers only are built without side input and without a projection between the passes of a looped block");
     if (m.d.norm_place == TI_SEQ_NORMS_BEHIND && (m.d.loop_times > 0 || m.d.side_dim > 0)) return fail("norms behind the sublayers only are built without a looped block and side input");
     return 0;
 }
@@ -474,6 +520,7 @@ std::vector<float> rotary_frequencies(const ti_seq_layer_desc& L) {
                 fi = (1.0 - s) * fi / L.rot_factor + s * fi;
             }
         }
+        if (L.rot_linear > 0.f) fi /= (double)L.rot_linear;
         f[i] = (float)fi;
     }
     return f;
@@ -689,6 +736,7 @@ int ensure_scratch(Model& m, int rows, int want) {
     if (rows > m.cap_rows) {
         const size_t R = (size_t)std::max(rows, 64), D = m.d.width;
         TRY(m.x.alloc(R * D));
+        if (m.n_streams > 0) TRY(m.xs.alloc(R * (size_t)m.n_streams * D));
         TRY(m.x0.alloc(R * D));
         if (m.d.loop_times > 0) TRY(m.xc.alloc(R * 2 * D));
         TRY(m.h.alloc(R * D));
@@ -895,8 +943,11 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     CK(cudaEventRecord(m.ev0, g_stream));
     const bool bf = m.d.mode == TI_SEQ_BF16;
     const int nt = 256;
-    if (bf) TRY(launch_dep(embed_rows_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, (const __nv_bfloat16*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr, (const float*)m.pos_freq.p));
-    else TRY(launch_dep(embed_rows_kernel<float>, dim3(T), dim3(nt), 0, (const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr, (const float*)m.pos_freq.p));
+    const bool front = m.d.norm_place == TI_SEQ_NORMS_FRONT;   // norms in front of the sublayers only: the residual lives in m.xs (one or more streams)
+    float* emb_out = front ? m.xs.p : m.x.p;
+    const int emb_copies = front ? m.n_streams : 1;
+    if (bf) TRY(launch_dep(embed_rows_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, (const __nv_bfloat16*)m.embed, sm, D, emb_out, m.loop_in ? m.x0.p : nullptr, (const float*)m.pos_freq.p, emb_copies));
+    else TRY(launch_dep(embed_rows_kernel<float>, dim3(T), dim3(nt), 0, (const float*)m.embed, sm, D, emb_out, m.loop_in ? m.x0.p : nullptr, (const float*)m.pos_freq.p, emb_copies));
     LAUNCHED();
     const float eps = m.d.norm_eps;
     const int gv = m.gvec;
@@ -909,6 +960,43 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         LAUNCHED();
         return 0;
     };
+    // norms in front only: sublayer `q` (0: mixer, 1: feed-forward) of layer run `ri` ends with its result in m.mo -- every stream is
+    // rewritten, and the input of the sublayer that follows (the same run's feed-forward or the next run's mixer) goes to m.h; the last
+    // sublayer of a run leaves the sum of the streams in m.x.  q < 0: nothing ends, the first sublayer of the step is opened.
+    auto hyper = [&](size_t ri, int q) -> int {
+        const LayerW& L = m.layers[m.runs[ri].layer];
+        HyperArgs a{};
+        a.X = m.xs.p; a.S = m.n_streams; a.D = D; a.gvec = gv; a.eps = eps; a.h = m.h.p;
+        const LayerW* next = nullptr;
+        int nq = 0;
+        if (q < 0) next = &L;
+        else {
+            a.y = m.mo.p; a.mix = L.hc_mix[q]; a.out = L.hc_out[q];
+            a.bias = q == 0 ? L.o_bias : nullptr;
+            if (q == 0 && L.d.ff > 0) { next = &L; nq = 1; }
+            else {
+                a.sum = m.x.p;
+                if (ri + 1 < m.runs.size()) next = &m.layers[m.runs[ri + 1].layer];
+            }
+        }
+        if (next) { a.in_next = next->hc_in[nq]; a.gain = nq == 0 ? next->norm1 : next->norm2; }
+        TRY(launch_dep(hyper_kernel, dim3(T), dim3(nt), 0, a));
+        LAUNCHED();
+        return 0;
+    };
+    // the short convolution in front of a sublayer: y = x + conv(x) over the sequence's last inputs; the slot then keeps the newest ones
+    auto short_conv = [&](const float* in, const float* w, int taps, float* state, float* out) -> int {
+        TRY(launch_dep(short_conv_kernel, dim3(T, T <= 64 ? (D + nt - 1) / nt : 1), dim3(nt), 0, in, sm, D, taps, w, state, out));
+        LAUNCHED();
+        bool many = false;   // (an entry of one row has shifted its state in the kernel above)
+        for (int e = 0; e < E; ++e) many = many || counts[e] > 1;
+        if (taps > 1 && many) {
+            TRY(launch_dep(short_conv_save_kernel, dim3(E, (D + nt - 1) / nt), dim3(nt), 0, in, sm, D, taps, state));
+            LAUNCHED();
+        }
+        return 0;
+    };
+    if (front) TRY(hyper(0, -1));
     // paged softmax attention of all rows of the step (prompt portions in tiles, the other rows one by one or split over their keys)
     auto attention = [&](const AttnShape& s, const float* q, const float* kp, const float* vp, float* out) -> int {
         const bool wide = std::max(s.dim, s.vdim) > 32 * kAttnMaxPerLane;
@@ -1040,29 +1128,22 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const bool attn = mixer == TI_SEQ_MIXER_ATTENTION;
         // decode steps (few rows) fuse the norm in front of the attention projections into the product's prologue
         const bool behind = m.d.norm_place == TI_SEQ_NORMS_BEHIND;   // the sublayers read the residual stream itself
-        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate && !behind && L.d.conv_taps < 1;
+        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate && !behind && !front && L.d.conv_taps < 1;
         // the mixers with ONE fused input projection (residual gate included) take the norm into that product's prologue as well
-        const bool fuse_front = few_rows(T, D) && (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2 || mixer == TI_SEQ_MIXER_LATENT) && !L.rg1;
+        const bool fuse_front = few_rows(T, D) && (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2 || mixer == TI_SEQ_MIXER_LATENT) && !L.rg1 && !front && L.d.conv_taps < 1;
         Fuse ff1;
         ff1.norm_gain = L.norm1; ff1.eps = eps; ff1.gvec = gv;
-        const float* front_in = fuse_front ? m.x.p : m.h.p;
         const Fuse* front_fuse = fuse_front ? &ff1 : nullptr;
-        if (!(fuse_rows && attn) && !fuse_front && !behind) {
-            TRY(launch_dep(rmsnorm_kernel, dim3(T), dim3(nt), 0, (const float*)m.x.p, (const int*)nullptr, D, L.norm1, gv, eps, m.h.p));
+        if (!(fuse_rows && attn) && !fuse_front && !behind && !front) {   // (with norms in front only, the sublayer before this one has left the input in m.h)
+            TRY(launch_dep(rmsnorm_kernel, dim3(T), dim3(nt), 0, (const float*)m.x.p, D, (const int*)nullptr, D, L.norm1, gv, eps, m.h.p));
             LAUNCHED();
         }
         const float* mix_in = behind ? m.x.p : m.h.p;   // what the mixer reads
-        if (L.d.conv_taps >= 1) {   // ... with the short convolution over the sequence's last inputs added; the slot then keeps the newest ones
-            TRY(launch_dep(short_conv_kernel, dim3(T, T <= 64 ? (D + nt - 1) / nt : 1), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, L.canon, R.conv_state.p, m.hc.p));
-            LAUNCHED();
-            bool many = false;   // (an entry of one row has shifted its state in the kernel above)
-            for (int e = 0; e < E; ++e) many = many || counts[e] > 1;
-            if (L.d.conv_taps > 1 && many) {
-                TRY(launch_dep(short_conv_save_kernel, dim3(E, (D + nt - 1) / nt), dim3(nt), 0, mix_in, sm, D, L.d.conv_taps, R.conv_state.p));
-                LAUNCHED();
-            }
+        if (L.d.conv_taps >= 1) {   // ... with the short convolution over the sequence's last inputs added
+            TRY(short_conv(mix_in, L.canon, L.d.conv_taps, R.conv_state.p, m.hc.p));
             mix_in = m.hc.p;
         }
+        const float* front_in = fuse_front ? m.x.p : mix_in;
         const float* gate1 = nullptr;   // residual gate of the mixer: pre-activations and their row stride
         int gate1_ld = 0;
         if (L.d.res_gate && L.rg1) {
@@ -1071,7 +1152,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             gate1_ld = D;
         } else if (L.d.res_gate) {
             gate1 = m.proj.p + L.off_rg1;
-            gate1_ld = L.n_front;
+            gate1_ld = L.ld_front;
         }
         if (attn) {
             AttnShape s{};
@@ -1086,6 +1167,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 TRY(gemm(m, mix_in, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
             }
             s.sink = L.sink; s.softcap = L.d.softcap; s.keep_first = L.d.keep_first; s.talk = L.talk;
+            s.rot_half = L.d.rot_half; s.v_norm = L.d.v_norm; s.bias = L.qkv_bias.p; s.temp = L.temp;
             if (L.d.qk_norm == TI_SEQ_QK_NORM_WHOLE) TRY(launch_dep(attn_prepare_whole_kernel, dim3(T), dim3(256), 0, m.proj.p, sm, s, L.qnorm, L.knorm, R.k_pool.p, R.v_pool.p));
             else TRY(launch_dep(attn_prepare_kernel, dim3(T), dim3(128), 0, m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p));
             LAUNCHED();
@@ -1170,18 +1252,33 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             LAUNCHED();
             TRY(gemm(m, m.att.p, Cv, L.o, m.mo.p, D, T, D, Cv));
         } else {   // latent attention
-            const int H = L.d.heads, d = L.d.dim, dr = L.d.rot_dims, dv = L.d.vdim, rank = L.d.kv_rank, kd = rank + dr, nf = L.n_front;
-            TRY(gemm(m, front_in, D, L.front, m.proj.p, nf, T, nf, D, EPI_NONE, 1.f, front_fuse));
+            const int H = L.d.heads, d = L.d.dim, dr = L.d.rot_dims, dv = L.d.vdim, rank = L.d.kv_rank, kd = rank + dr, nf = L.ld_front;
+            TRY(gemm(m, front_in, D, L.front, m.proj.p, nf, T, L.n_front, D, EPI_NONE, 1.f, front_fuse));
+            if (L.d.q_rank > 0) {   // q = Uq norm(Dq h): the norm rides in the second product's prologue when the rows are few
+                const int qr = L.d.q_rank, nq = H * (d + dr);
+                if (few_rows(T, qr)) {
+                    Fuse f;
+                    f.norm_gain = L.dqnorm; f.eps = eps; f.gvec = 1;
+                    TRY(gemm(m, m.proj.p + L.off_dq, nf, L.uq, m.proj.p + L.off_q, nf, T, nq, qr, EPI_NONE, 1.f, &f));
+                } else {
+                    TRY(launch_dep(rmsnorm_kernel, dim3(T), dim3(nt), 0, (const float*)(m.proj.p + L.off_dq), nf, (const int*)nullptr, qr, L.dqnorm, 1, eps, m.lora.p));
+                    LAUNCHED();
+                    TRY(gemm(m, m.lora.p, qr, L.uq, m.proj.p + L.off_q, nf, T, nq, qr));
+                }
+            }
             float* pool = R.kv_run >= 0 ? m.runs[R.kv_run].k_pool.p : R.k_pool.p;
             LatentShape ls{};
             ls.heads = H; ls.dim = d; ls.rot = dr; ls.rank = rank; ls.ld = nf; ls.off_q = L.off_q; ls.off_dkv = L.off_dkv; ls.eps = eps;
+            ls.rot_half = L.d.rot_half;
             TRY(launch_dep(latent_prepare_kernel, dim3(T), dim3(128), 0, (const float*)m.proj.p, sm, ls, (const float*)L.inv_freq.p, L.cnorm, pool, m.aux.p));
             LAUNCHED();
             // the key up-projection moves to the query: qabs[t][h][0 .. rank) = Uk_h^T q_h
             TRY(gemm_heads(m, m.proj.p + L.off_q, nf, d + dr, L.ukT.p, m.aux.p, H * kd, kd, H, T, rank, d));
             AttnShape s{};
-            s.heads = H; s.kv_heads = 1; s.dim = kd; s.vdim = rank; s.window = 0; s.rot_dims = 0; s.qk_norm = 0; s.out_gate = 0;
+            s.heads = H; s.kv_heads = 1; s.dim = kd; s.vdim = rank; s.window = L.d.window; s.rot_dims = 0; s.qk_norm = 0;
             s.scale = L.d.scale; s.eps = eps; s.ld = H * kd; s.v_ld = kd; s.sink = L.sink;
+            // (the gate is one number a head: it commutes with the value up-projection behind the weighted sum)
+            s.out_gate = L.d.out_gate; s.gate = L.d.out_gate ? m.proj.p + L.off_g : nullptr; s.gate_ld = nf;
             TRY(attention(s, m.aux.p, pool, pool, m.aux2.p));
             // ... and the value up-projection behind the weighted sum: att[t][h] = Uv_h (sum_j p_j c_j)
             TRY(gemm_heads(m, m.aux2.p, H * rank, rank, L.uv, m.att.p, H * dv, dv, H, T, dv, rank));
@@ -1189,8 +1286,13 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         }
         if (L.d.ff > 0) {
             const bool fuse_ff = fuse_rows && L.d.ff_kind == TI_SEQ_FF_GLU;
-            TRY(post(L.norm1b, gv, (fuse_ff || behind) ? nullptr : L.norm2, gate1, gate1_ld, L.rg1b, nullptr));
+            if (front) TRY(hyper(ri, 0));
+            else TRY(post(L.norm1b, gv, (fuse_ff || behind) ? nullptr : L.norm2, gate1, gate1_ld, L.rg1b, nullptr));
             const float* ff_in = behind ? m.x.p : m.h.p;   // what the feed-forward reads
+            if (L.canon2) {
+                TRY(short_conv(ff_in, L.canon2, L.d.conv_taps, R.conv_state2.p, m.hc.p));
+                ff_in = m.hc.p;
+            }
             const float* gate2 = nullptr;
             int gate2_ld = 0;
             if (L.d.res_gate && L.rg2) {
@@ -1212,8 +1314,12 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                     Fuse f;
                     f.norm_gain = L.norm2; f.eps = eps; f.gvec = gv; f.glu_ff = F; f.glu_act = L.d.ff_act;
                     TRY(gemm(m, m.x.p, D, L.gateup, m.act.p, F, T, F, D, EPI_NONE, 1.f, &f));
+                } else if (few_rows(T, D)) {   // [gate | up] -> act(gate) * up in one launch
+                    Fuse f;
+                    f.glu_ff = F; f.glu_act = L.d.ff_act;
+                    TRY(gemm(m, ff_in, D, L.gateup, m.act.p, F, T, F, D, EPI_NONE, 1.f, &f));
                 } else {
-                    TRY(gemm(m, m.h.p, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
+                    TRY(gemm(m, ff_in, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
                     glu_kernel<<<grid_for((size_t)T * F), 256, 0, g_stream>>>(m.proj.p, F, L.d.ff_act, m.act.p, (size_t)T * F);
                     LAUNCHED();
                 }
@@ -1263,7 +1369,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             if (down_done) {}
             else if (L.ff_width > 0) TRY(gemm(m, m.act.p, L.ff_width, L.down, m.mo.p, D, T, D, L.ff_width));
             else CK(cudaMemsetAsync(m.mo.p, 0, (size_t)T * D * sizeof(float), g_stream));
-            TRY(post(L.norm2b, gv, nullptr, gate2, gate2_ld, L.rg2b, idw));
+            if (front) TRY(hyper(ri, 1));
+            else TRY(post(L.norm2b, gv, nullptr, gate2, gate2_ld, L.rg2b, idw));
+        } else if (front) {
+            TRY(hyper(ri, 0));
         } else {
             TRY(post(L.norm1b, gv, nullptr, gate1, gate1_ld, L.rg1b, nullptr));
         }
@@ -1290,7 +1399,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             f.norm_gain = m.final_norm; f.eps = eps; f.gvec = m.gvec;
             TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, head_epi, head_alpha, &f));
         } else {
-            TRY(launch_dep(rmsnorm_kernel, dim3(n_out), dim3(nt), 0, (const float*)m.x.p, d_out, D, m.final_norm, m.gvec, eps, m.hn.p));
+            TRY(launch_dep(rmsnorm_kernel, dim3(n_out), dim3(nt), 0, (const float*)m.x.p, D, d_out, D, m.final_norm, m.gvec, eps, m.hn.p));
             LAUNCHED();
             TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, head_epi, head_alpha));
         }
@@ -1433,7 +1542,7 @@ int ti_seq_model_new(const ti_seq_model_desc* desc, const ti_seq_layer_desc* lay
     if (desc->loop_times > 0) {
         for (int i = 0; i < desc->loop_start; ++i) add_run(i, false);
         for (int t = 0; t < desc->loop_times; ++t)
-            for (int i = desc->loop_start; i < desc->loop_stop; ++i) add_run(i, i == desc->loop_start);
+            for (int i = desc->loop_start; i < desc->loop_stop; ++i) add_run(i, i == desc->loop_start && !desc->loop_plain);
         for (int i = desc->loop_stop; i < desc->n_layers; ++i) add_run(i, false);
     } else {
         for (int i = 0; i < desc->n_layers; ++i) add_run(i, false);
@@ -1547,9 +1656,16 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
         CK(cudaMemcpy(m.pos_freq.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
     }
     if (m.d.side_dim > 0) m.side_embed = P("side.embed");
-    if (m.d.loop_times > 0) m.loop_in = P("loop.in");
-    m.gvec = m.d.norm_kind == TI_SEQ_NORM_ONE_PLUS ? 1 : 0;
-    if (m.gvec) {   // gains stored around zero and applied as 1 + w: converted once
+    if (m.d.loop_times > 0 && !m.d.loop_plain) m.loop_in = P("loop.in");
+    m.gvec = m.d.norm_kind != TI_SEQ_NORM_SCALAR ? 1 : 0;
+    const bool front = m.d.norm_place == TI_SEQ_NORMS_FRONT;
+    if (front) {   // one stream with in = mix = out = 1 is the plain residual x <- x + y
+        m.n_streams = std::max(1, m.d.streams);
+        const float one[1] = {1.f};
+        TRY(m.ones.alloc(1));
+        CK(cudaMemcpy(m.ones.p, one, sizeof(one), cudaMemcpyHostToDevice));
+    }
+    if (m.d.norm_kind == TI_SEQ_NORM_ONE_PLUS) {   // gains stored around zero and applied as 1 + w: converted once
         std::vector<std::string> names{"final.norm"};
         for (int i = 0; i < m.d.n_layers; ++i)
             for (const char* sfx : {"norm1", "norm1b", "norm2", "norm2b"}) names.push_back("l" + std::to_string(i) + "." + sfx);
@@ -1584,8 +1700,22 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
         LayerW& L = m.layers[i];
         const std::string p = "l" + std::to_string(i) + ".";
         if (behind) L.norm1b = F(p + "norm1");   // the only norm of the sublayer sits behind it
+        else if (front) L.norm1 = F(p + "norm1");
         else { L.norm1 = F(p + "norm1"); L.norm1b = F(p + "norm1b"); }
         if (L.d.conv_taps >= 1) { L.canon = F(p + "canon1"); m.any_conv = true; }
+        if (L.d.conv_ff && L.d.ff > 0) L.canon2 = F(p + "canon2");
+        for (int q = 0; q < 2 && front; ++q) {
+            if (q == 1 && L.d.ff <= 0) break;
+            const std::string hc = p + "hc" + std::to_string(q + 1) + ".";
+            L.hc_in[q] = m.d.streams > 0 ? F(hc + "in") : m.ones.p;
+            L.hc_out[q] = m.d.streams > 0 ? F(hc + "out") : m.ones.p;
+            L.hc_mix[q] = m.d.streams > 0 ? F(hc + "mix") : m.ones.p;
+        }
+        if (L.d.sink == TI_SEQ_SINK_ZERO) {
+            TRY(L.sink_zero.alloc((size_t)L.d.heads));
+            CK(cudaMemset(L.sink_zero.p, 0, (size_t)L.d.heads * sizeof(float)));
+            L.sink = L.sink_zero.p;
+        }
         bool rg1_fused = false, rg2_fused = false;
         if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
             TRY(concat_rows(m, {T(p + "mix.q"), T(p + "mix.k"), T(p + "mix.v"), L.d.out_gate ? T(p + "mix.g") : nullptr}, L.qkvg_buf, &L.n_qkvg));
@@ -1600,7 +1730,16 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             m.max_heads_v = std::max(m.max_heads_v, L.d.heads * (L.d.vdim + 2));
             if (L.d.qk_norm == TI_SEQ_QK_NORM_WHOLE) { L.qnorm = F(p + "mix.q.norm"); L.knorm = F(p + "mix.k.norm"); }
             if (L.d.talk) L.talk = F(p + "mix.talk");
-            if (L.d.sink) L.sink = F(p + "mix.sink");
+            if (L.d.sink == TI_SEQ_SINK_LEARNED) L.sink = F(p + "mix.sink");
+            if (L.d.head_temp) L.temp = F(p + "mix.temp");
+            if (L.d.proj_bias) {   // the three biases side by side, as the fused product lays its columns out
+                const size_t nq = (size_t)L.d.heads * L.d.dim, nk = (size_t)L.d.kv_heads * L.d.dim, nv = (size_t)L.d.kv_heads * L.d.vdim;
+                TRY(L.qkv_bias.alloc(nq + nk + nv));
+                CK(cudaMemcpy(L.qkv_bias.p, F(p + "mix.q.b"), nq * sizeof(float), cudaMemcpyDeviceToDevice));
+                CK(cudaMemcpy(L.qkv_bias.p + nq, F(p + "mix.k.b"), nk * sizeof(float), cudaMemcpyDeviceToDevice));
+                CK(cudaMemcpy(L.qkv_bias.p + nq + nk, F(p + "mix.v.b"), nv * sizeof(float), cudaMemcpyDeviceToDevice));
+                L.o_bias = F(p + "mix.o.b");
+            }
             if (L.d.talk || L.d.softcap > 0.f || L.d.keep_first > 0) {
                 const int H = L.d.heads, d4 = (L.d.dim + 3) / 4 * 4, dv4 = (L.d.vdim + 3) / 4 * 4;
                 L.mix_HP = H <= 8 ? 8 : H <= 16 ? 16 : H <= 32 ? 32 : 64;
@@ -1643,18 +1782,30 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             }
             L.normw = F(p + "mix.norm");
             L.o = P(p + "mix.o");
+            L.ld_front = L.n_front;
             m.max_proj = std::max(m.max_proj, L.n_front);
             m.max_att = std::max(m.max_att, Cv);
         } else {   // latent attention
             const int H = L.d.heads, kd = L.d.kv_rank + L.d.rot_dims;
             std::vector<int> off;
-            TRY(concat_rows(m, {T(p + "mix.q"), L.d.kv_from < 0 ? T(p + "mix.dkv") : nullptr, L.d.res_gate ? T(p + "rg1") : nullptr}, L.front_buf, &L.n_front, &off));
+            TRY(concat_rows(m, {T(p + (L.d.q_rank > 0 ? "mix.dq" : "mix.q")), L.d.kv_from < 0 ? T(p + "mix.dkv") : nullptr, L.d.res_gate ? T(p + "rg1") : nullptr,
+                                L.d.out_gate ? T(p + "mix.g") : nullptr}, L.front_buf, &L.n_front, &off));
             L.front = L.front_buf.p;
-            L.off_q = off[0]; L.off_dkv = off[1]; L.off_rg1 = off[2];
+            L.off_q = off[0]; L.off_dkv = off[1]; L.off_rg1 = off[2]; L.off_g = off[3];
+            L.ld_front = L.n_front;
+            if (L.d.q_rank > 0) {   // the queries come from a second product and sit behind the first one's columns
+                L.off_dq = off[0];
+                L.off_q = L.n_front;
+                L.ld_front = L.n_front + H * (L.d.dim + L.d.rot_dims);
+                L.uq = P(p + "mix.uq");
+                L.dqnorm = F(p + "mix.dq.norm");
+                note_k(L.d.q_rank);
+                m.max_rank = std::max(m.max_rank, L.d.q_rank);
+            }
             rg1_fused = L.d.res_gate != 0;
-            for (const char* s : {"mix.q", "mix.dkv", "rg1"}) release(p + s);
+            for (const char* s : {"mix.q", "mix.dq", "mix.dkv", "rg1", "mix.g"}) release(p + s);
             if (L.d.kv_from < 0) L.cnorm = F(p + "mix.dkv.norm");
-            if (L.d.sink) L.sink = F(p + "mix.sink");
+            if (L.d.sink == TI_SEQ_SINK_LEARNED) L.sink = F(p + "mix.sink");
             TRY(L.ukT.alloc((size_t)H * L.d.dim * L.d.kv_rank * m.wsize));
             const size_t n = (size_t)H * L.d.dim * L.d.kv_rank;
             if (m.d.mode == TI_SEQ_BF16)
@@ -1673,7 +1824,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             if (!f.empty()) CK(cudaMemcpy(L.inv_freq.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
             note_k(L.d.dim);
             note_k(L.d.kv_rank);
-            m.max_proj = std::max(m.max_proj, L.n_front);
+            m.max_proj = std::max(m.max_proj, L.ld_front);
             m.max_att = std::max(m.max_att, H * L.d.vdim);
             m.max_aux = std::max(m.max_aux, H * kd);
             m.max_aux2 = std::max(m.max_aux2, H * L.d.kv_rank);
@@ -1685,6 +1836,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
         }
         if (L.d.ff > 0) {
             if (behind) L.norm2b = F(p + "norm2");
+            else if (front) L.norm2 = F(p + "norm2");
             else { L.norm2 = F(p + "norm2"); L.norm2b = F(p + "norm2b"); }
             if (L.d.ff_kind == TI_SEQ_FF_DENSE) {
                 L.ffront = P(p + "mlp.up");
@@ -1801,6 +1953,10 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
         if (L.conv_taps > 1) {
             TRY(R.conv_state.alloc((size_t)m.d.max_seqs * (L.conv_taps - 1) * D));
             CK(cudaMemset(R.conv_state.p, 0, R.conv_state.n * sizeof(float)));
+            if (L.conv_ff && L.ff > 0) {
+                TRY(R.conv_state2.alloc((size_t)m.d.max_seqs * (L.conv_taps - 1) * D));
+                CK(cudaMemset(R.conv_state2.p, 0, R.conv_state2.n * sizeof(float)));
+            }
         }
     }
     m.max_k = std::max({m.max_k, 2 * D, m.max_att, m.max_ff, m.max_rank, D});
@@ -1996,13 +2152,12 @@ int ti_seq_model_bytes(ti_seq_model_t h, double* weight_bytes, double* kv_bytes_
     if (!m || !m->finalized) return fail("bad model handle");
     double w = 0, kv = 0, st = 0;
     const double D = m->d.width, ws = (double)m->wsize;
-    if (m->d.loop_times > 0) w += 2 * D * D * ws * m->d.loop_times;
+    if (m->d.loop_times > 0 && !m->d.loop_plain) w += 2 * D * D * ws * m->d.loop_times;
     for (const Run& R : m->runs) {
         const ti_seq_layer_desc& L = m->layers[R.layer].d;
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             w += ((double)L.heads * L.dim + (double)L.kv_heads * (L.dim + L.vdim) + (L.out_gate ? L.heads : 0) + (double)L.heads * L.vdim) * D * ws;
             kv += (double)L.kv_heads * (L.dim + L.vdim) * 4;
-            if (L.conv_taps > 1) st += (double)(L.conv_taps - 1) * D * 4;
         } else if (L.mixer == TI_SEQ_MIXER_WKV) {
             const double C = (double)L.heads * L.dim;
             w += (5 * C * D + (double)L.decay_rank * (D + C)) * ws;
@@ -2014,12 +2169,14 @@ int ti_seq_model_bytes(ti_seq_model_t h, double* weight_bytes, double* kv_bytes_
             st += (double)L.heads * L.dim * L.vdim * 4;
         } else {
             const double H = L.heads;
-            w += (H * (L.dim + L.rot_dims) * D + H * (L.dim + L.vdim) * L.kv_rank + H * L.vdim * D) * ws;
+            w += (H * (L.dim + L.vdim) * L.kv_rank + H * L.vdim * D + (L.out_gate ? H * D : 0.0)) * ws;
+            w += (L.q_rank > 0 ? (double)L.q_rank * (D + H * (L.dim + L.rot_dims)) : H * (L.dim + L.rot_dims) * D) * ws;
             if (L.kv_from < 0) {
                 w += (double)(L.kv_rank + L.rot_dims) * D * ws;
                 kv += (double)(L.kv_rank + L.rot_dims) * 4;
             }
         }
+        if (L.conv_taps > 1) st += (double)(L.conv_taps - 1) * D * 4 * (L.conv_ff && L.ff > 0 ? 2 : 1);
         if (L.res_gate) w += (L.ff > 0 ? 2.0 : 1.0) * D * D * ws;
         if (L.ff > 0) {
             // routed experts: the stacked products read every expert's weights whatever the tokens chose

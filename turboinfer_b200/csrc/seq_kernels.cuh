@@ -52,9 +52,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 // ---- embedding -----------------------------------------------------------------------------------------------------
 // x[t] = embed[tok[t]] (+ the sinusoidal position vector: entry 2i = sin(pos * pos_freq[i]), entry 2i + 1 = cos of the same angle,
-// angle and functions in fp32); x0 (optional) keeps the embedding output for the looped block's input projection
+// angle and functions in fp32); x0 (optional) keeps the embedding output for the looped block's input projection; copies > 1: the row
+// is written that many times in a row (x [T][copies][D]: the streams of hyper-connections all start from the embedding output)
 template <typename WT>
-__global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0, const float* pos_freq) {
+__global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0, const float* pos_freq, int copies) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
@@ -66,7 +67,7 @@ __global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, fl
             const float ang = pos * pos_freq[d >> 1];
             v += (d & 1) ? cosf(ang) : sinf(ang);
         }
-        x[(size_t)t * D + d] = v;
+        for (int c = 0; c < copies; ++c) x[((size_t)t * copies + c) * D + d] = v;
         if (x0) x0[(size_t)t * D + d] = v;
     }
 }
@@ -84,13 +85,14 @@ __global__ void concat_rows_kernel(const float* x, const float* x0, int D, float
 // ---- RMS norms -------------------------------------------------------------------------------------------------------------
 // The gain is one number for all coordinates (gvec = 0: gain[0]) or one per coordinate (gvec = 1: gain[d]; a design that stores
 // its gains around zero and applies 1 + w has them converted once when the model is finalized).
-// y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain; rows (optional) gathers (the rows whose logits are wanted)
-__global__ void rmsnorm_kernel(const float* x, const int* rows, int D, const float* gain, int gvec, float eps, float* y) {
+// y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain; rows (optional) gathers (the rows whose logits are wanted); ldx = row stride of x
+// (a slice of a wider projection output)
+__global__ void rmsnorm_kernel(const float* x, int ldx, const int* rows, int D, const float* gain, int gvec, float eps, float* y) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     __shared__ float red[32];
     const int t = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[t] : t) * D;
+    const float* xr = x + (size_t)(rows ? rows[t] : t) * ldx;
     float ss = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) ss += xr[d] * xr[d];
     ss = block_sum(ss, red);
@@ -697,7 +699,22 @@ struct AttnShape {
     float softcap;                    // > 0: score <- cap * tanh(score / cap) after scaling
     int keep_first;                   // with a window: keys at positions < keep_first stay visible
     const float* talk;                // [heads][heads] or null: score_h <- sum_g talk[h][g] score_g before masking
+    // read by attn_prepare_kernel: what happens to the projections before they are used / cached
+    int rot_half;                     // 1: rotated coordinate i pairs with i + rot_dims / 2 instead of (2 i, 2 i + 1)
+    int v_norm;                       // 1: every value head is divided by its RMS (no weight) before it is cached
+    const float* bias;                // [ld columns of q | k | v] or null: added to the projections first
+    const float* temp;                // [heads] or null: query head h is multiplied by temp[h] (a per-head factor of its scores)
+    // the output gate's pre-activations when they are not part of the fused projection: gate[t * gate_ld + h] (null: behind q | k | v)
+    const float* gate;
+    int gate_ld;
 };
+// sigmoid output gate of (row t, head h), 1 without a gate
+__device__ __forceinline__ float attn_gate(const AttnShape& s, const float* qkvg, int t, int h) {
+    if (!s.out_gate) return 1.f;
+    const float z = s.gate ? s.gate[(size_t)t * s.gate_ld + h]
+                           : qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
+    return 1.f / (1.f + expf(-z));
+}
 __device__ __forceinline__ size_t attn_vstride(const AttnShape& s) { return s.v_ld ? (size_t)s.v_ld : (size_t)s.kv_heads * s.vdim; }
 // the end of a softmax with a sink: (max, sum) -> the factor for the accumulated weighted values
 __device__ __forceinline__ float attn_finish_factor(const AttnShape& s, int h, float mx, float l) {
@@ -705,8 +722,9 @@ __device__ __forceinline__ float attn_finish_factor(const AttnShape& s, int h, f
     const float sk = s.sink[h], m2 = fmaxf(mx, sk), c = expf(mx - m2);
     return c / (l * c + expf(sk - m2));
 }
-// Rotation of q and k, unit RMS per head, and the cache append: one block per row.  q is rewritten in place; k and v go
-// to the row's page.  inv_freq[rot_dims / 2] holds the (scaled) frequencies; the angle is position * frequency in fp32.
+// Biases, rotation of q and k, unit RMS per head, the per-head query factor, unit-RMS values and the cache append: one block per
+// row.  q is rewritten in place; k and v go to the row's page.  inv_freq[rot_dims / 2] holds the (scaled) frequencies; the angle is
+// position * frequency in fp32.  Pair i of the rotated coordinates is (2 i, 2 i + 1) or, with rot_half, (i, i + rot_dims / 2).
 __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const float* inv_freq, float* k_pool, float* v_pool) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
@@ -717,37 +735,54 @@ __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const 
     const size_t tok_off = (size_t)page * kPageTokens + pos % kPageTokens;
     float* row = qkvg + (size_t)t * s.ld;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int nqk = s.heads + s.kv_heads;
+    const int nqk = s.heads + s.kv_heads, half = s.rot_dims / 2;
     for (int h = warp; h < nqk; h += nw) {
         float* v = row + (size_t)h * s.dim;   // q heads first, k heads right behind them
+        const float* b = s.bias ? s.bias + (size_t)h * s.dim : nullptr;
         float ss = 0.f;
-        for (int i = lane; i < s.dim / 2 + (s.dim & 1); i += 32) {
-            float a = v[2 * i], b = (2 * i + 1 < s.dim) ? v[2 * i + 1] : 0.f;
-            if (2 * i + 1 < s.rot_dims) {
-                const float ang = (float)pos * inv_freq[i];
-                float sn, cs;
-                sincosf(ang, &sn, &cs);
-                const float ra = a * cs - b * sn, rb = b * cs + a * sn;
-                a = ra;
-                b = rb;
-            }
-            v[2 * i] = a;
-            if (2 * i + 1 < s.dim) v[2 * i + 1] = b;
-            ss += a * a + b * b;
+        for (int i = lane; i < half; i += 32) {
+            const int i0 = s.rot_half ? i : 2 * i, i1 = s.rot_half ? i + half : 2 * i + 1;
+            const float a = v[i0] + (b ? b[i0] : 0.f), c = v[i1] + (b ? b[i1] : 0.f);
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float ra = a * cs - c * sn, rc = c * cs + a * sn;
+            v[i0] = ra;
+            v[i1] = rc;
+            ss += ra * ra + rc * rc;
+        }
+        for (int i = 2 * half + lane; i < s.dim; i += 32) {
+            const float a = v[i] + (b ? b[i] : 0.f);
+            v[i] = a;
+            ss += a * a;
         }
         ss = warp_sum(ss);
-        const float sc = s.qk_norm ? 1.f / sqrtf(ss / (float)s.dim + s.eps) : 1.f;
+        float sc = s.qk_norm ? 1.f / sqrtf(ss / (float)s.dim + s.eps) : 1.f;
         __syncwarp();
         if (h < s.heads) {
-            for (int i = lane; i < s.dim; i += 32) v[i] *= sc;
+            if (s.temp) sc *= s.temp[h];
+            if (s.qk_norm || s.temp)
+                for (int i = lane; i < s.dim; i += 32) v[i] *= sc;
         } else {
             float* kd = k_pool + tok_off * (size_t)(s.kv_heads * s.dim) + (size_t)(h - s.heads) * s.dim;
             for (int i = lane; i < s.dim; i += 32) kd[i] = v[i] * sc;
         }
     }
     const float* vs = row + (size_t)nqk * s.dim;
+    const float* vb = s.bias ? s.bias + (size_t)nqk * s.dim : nullptr;
     float* vd = v_pool + tok_off * (size_t)(s.kv_heads * s.vdim);
-    for (int i = threadIdx.x; i < s.kv_heads * s.vdim; i += blockDim.x) vd[i] = vs[i];
+    if (s.v_norm) {
+        for (int g = warp; g < s.kv_heads; g += nw) {
+            float ss = 0.f;
+            for (int i = lane; i < s.vdim; i += 32) {
+                const float a = vs[g * s.vdim + i] + (vb ? vb[g * s.vdim + i] : 0.f);
+                ss += a * a;
+            }
+            const float sc = 1.f / sqrtf(warp_sum(ss) / (float)s.vdim + s.eps);
+            for (int i = lane; i < s.vdim; i += 32) vd[g * s.vdim + i] = (vs[g * s.vdim + i] + (vb ? vb[g * s.vdim + i] : 0.f)) * sc;
+        }
+    } else {
+        for (int i = threadIdx.x; i < s.kv_heads * s.vdim; i += blockDim.x) vd[i] = vs[i] + (vb ? vb[i] : 0.f);
+    }
 }
 
 // Softmax attention of one (row, query head) over the keys its window allows, read from the paged cache: 4 warps share the
@@ -820,12 +855,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const
         f[w] = (pm[w] == -INFINITY) ? 0.f : expf(pm[w] - M);
         L += pl[w] * f[w];
     }
-    float gate = 1.f;
-    if (s.out_gate) {
-        const float z = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
-        gate = 1.f / (1.f + expf(-z));
-    }
-    const float fin = attn_finish_factor(s, h, M, L) * gate;
+    const float fin = attn_finish_factor(s, h, M, L) * attn_gate(s, qkvg, t, h);
     for (int d = threadIdx.x; d < s.vdim; d += blockDim.x) {
         float acc = 0.f;
         for (int w = 0; w < kAttnWarps; ++w) acc += po[w * s.vdim + d] * f[w];
@@ -962,12 +992,7 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
         const int r = ty + 16 * i;
         if (r >= n) continue;
         const int t = row0 + r;
-        float gate = 1.f;
-        if (s.out_gate) {
-            const float z = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * d + (size_t)s.kv_heads * dv + h];
-            gate = 1.f / (1.f + expf(-z));
-        }
-        const float f = gate * attn_finish_factor(s, h, mrow[i], lrow[i]);
+        const float f = attn_gate(s, qkvg, t, h) * attn_finish_factor(s, h, mrow[i], lrow[i]);
 #pragma unroll
         for (int jj = 0; jj < DV4; ++jj) {
             const int col = tx * 4 + 64 * jj;

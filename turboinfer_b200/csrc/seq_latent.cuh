@@ -21,10 +21,11 @@ struct LatentShape {
     int off_q, off_dkv;          // column of q (heads * (dim + rot)) and of the down projection (rank + rot); off_dkv < 0: the layer
                                  // reads another layer's cache and appends nothing
     float eps;
+    int rot_half;                // 1: rotated coordinate i pairs with i + rot / 2 instead of (2 i, 2 i + 1)
 };
 // One block per row.  Own cache: c = dkv[:rank] / rms * cnorm -> page row; rotated key part -> behind it.  Every head's rotated
-// query part -> qabs[t][h][rank ...] (the absorbed part [0, rank) is written by the product with Uk^T).  Pairs (2i, 2i + 1) of
-// the rotated parts turn by position * inv_freq[i], angle in fp32.
+// query part -> qabs[t][h][rank ...] (the absorbed part [0, rank) is written by the product with Uk^T).  Pair i of the rotated
+// parts -- (2i, 2i + 1), or (i, i + rot / 2) with rot_half -- turns by position * inv_freq[i], angle in fp32.
 __global__ void latent_prepare_kernel(const float* proj, StepMeta m, LatentShape s, const float* inv_freq, const float* cnorm, float* pool, float* qabs) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
@@ -45,9 +46,10 @@ __global__ void latent_prepare_kernel(const float* proj, StepMeta m, LatentShape
         for (int i = threadIdx.x; i < s.rot / 2; i += blockDim.x) {
             float sn, cs;
             sincosf((float)pos * inv_freq[i], &sn, &cs);
-            const float a = src[s.rank + 2 * i], b = src[s.rank + 2 * i + 1];
-            dst[s.rank + 2 * i] = a * cs - b * sn;
-            dst[s.rank + 2 * i + 1] = b * cs + a * sn;
+            const int i0 = s.rot_half ? i : 2 * i, i1 = s.rot_half ? i + s.rot / 2 : 2 * i + 1;
+            const float a = src[s.rank + i0], b = src[s.rank + i1];
+            dst[s.rank + i0] = a * cs - b * sn;
+            dst[s.rank + i1] = b * cs + a * sn;
         }
     }
     for (int x = threadIdx.x; x < s.heads * (s.rot / 2); x += blockDim.x) {
@@ -56,9 +58,10 @@ __global__ void latent_prepare_kernel(const float* proj, StepMeta m, LatentShape
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         const float* q = row + s.off_q + (size_t)h * (s.dim + s.rot) + s.dim;
         float* dst = qabs + ((size_t)t * s.heads + h) * kd + s.rank;
-        const float a = q[2 * i], b = q[2 * i + 1];
-        dst[2 * i] = a * cs - b * sn;
-        dst[2 * i + 1] = b * cs + a * sn;
+        const int i0 = s.rot_half ? i : 2 * i, i1 = s.rot_half ? i + s.rot / 2 : 2 * i + 1;
+        const float a = q[i0], b = q[i1];
+        dst[i0] = a * cs - b * sn;
+        dst[i1] = b * cs + a * sn;
     }
 }
 // Uk [heads * dim][rank] -> per head its transpose [heads][rank][dim]: the weight of the query-side product

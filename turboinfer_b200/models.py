@@ -15,6 +15,11 @@ reads folder/config.json and folder/model.safetensors.  Registered architectures
                   the heads, a sliding window that keeps the first keys, a softmax sink; dense feed-forward with the xIELU
                   activation or routed experts chosen by biased logits with a plain shared expert; sinusoidal positions added to
                   the embedding, logits tied to the embedding table; runs on the layered sequence engine too.
+  * "Zopipel"  -- pre-norm layers on hyper-connections (several residual streams that every sublayer reads as one mixture and
+                  rewrites together), a short causal convolution in front of BOTH sublayers, grouped attention with biased
+                  projections, half-split rotation with linearly scaled frequencies, unit-RMS values, a per-head score factor and a
+                  zero-score sink, latent attention with low-rank queries, a sliding window and a per-head output gate, a gated
+                  gelu feed-forward, and a block of layers that is run several times in a row; on the layered sequence engine too.
   * "llama"    -- the quantized Llama-style decoder of the persistent decode kernel (turboinfer_b200.capi.Model); built from
                   {"hidden", "layers", "heads", "inter", "vocab"} and fp32 tensors under the reference's names.
 """
@@ -226,6 +231,73 @@ def gulazen_descs(cfg: dict, mode: int, max_tokens: int, max_seqs: int, tensor_s
 def _load_gulazen(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seqs: int):
     mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
     desc, layers = gulazen_descs(cfg, mode, max_tokens, max_seqs)
+    return _seq.SeqModel(desc, layers).load(weights)
+
+
+def zopipel_descs(cfg: dict, mode: int, max_tokens: int, max_seqs: int, tensor_shapes: Dict[str, Tuple[int, ...]] = None):
+    """config.json of a Zopipel model -> (ModelDesc, [LayerDesc]).  Every size and constant comes from the configuration."""
+    taps = int(_req(_req(cfg, "canon", "the model"), "taps", "canon"))
+    if taps < 1:
+        raise ValueError(f"config: canon.taps {taps}")
+    layers: List[_seq.LayerDesc] = []
+    for i, L in enumerate(_req(cfg, "layers", "the model")):
+        where = f"layer {i}"
+        kind = _req(L, "type", where)
+        mx = _req(L, "mixer", where)
+        d = _seq.LayerDesc()
+        d.heads = int(_req(mx, "heads", where))
+        d.dim, d.vdim = int(_req(mx, "dim", where)), int(_req(mx, "vdim", where))
+        d.scale = float(_req(mx, "scale", where))
+        rot = _req(mx, "rot", where)
+        d.rot_dims, d.rot_base, d.rot_half = int(_req(rot, "dims", where + " rot")), float(_req(rot, "base", where + " rot")), 1
+        sc = rot.get("scaling")
+        if sc:
+            d.rot_linear = float(_req(sc, "factor", where + " rot.scaling"))
+        mask = mx.get("mask")
+        d.window = int(_req(mask, "size", where + " mask")) if mask else 0
+        if mask and d.window < 1:
+            raise ValueError(f"{where}: mask.size {d.window}")
+        if kind == "attention":
+            d.mixer = _seq.MIXER_ATTENTION
+            d.kv_heads = int(_req(mx, "kv_heads", where))
+            d.proj_bias, d.v_norm, d.head_temp, d.sink = 1, 1, 1, _seq.SINK_ZERO
+        elif kind == "latent_attention":
+            d.mixer = _seq.MIXER_LATENT
+            d.kv_heads = d.heads
+            d.kv_rank, d.q_rank = int(_req(mx, "kv_rank", where)), int(_req(mx, "q_rank", where))
+            if int(_req(mx, "rot_dim", where)) != d.rot_dims:
+                raise ValueError(f"{where}: rot.dims {d.rot_dims} differs from rot_dim {mx['rot_dim']}; the rotated part turns as a whole")
+            d.out_gate, d.sink = 1, _seq.SINK_NONE
+        else:
+            raise ValueError(f"{where}: unknown mixer type '{kind}'")
+        d.conv_taps, d.conv_ff = taps, 1
+        mlp = L.get("mlp")
+        if mlp:
+            if _req(mlp, "kind", where + " mlp") != "dense":
+                raise ValueError(f"{where}: unknown feed-forward kind '{mlp.get('kind')}'")
+            d.ff_kind, d.ff, d.ff_act = _seq.FF_GLU, int(_req(mlp, "ff", where + " mlp")), _seq.ACT_GELU_TANH
+        layers.append(d)
+    m = _seq.ModelDesc()
+    m.vocab, m.width, m.n_layers = int(_req(cfg, "vocab", "the model")), int(_req(cfg, "width", "the model")), len(layers)
+    lp = cfg.get("loop")
+    if lp and int(lp.get("times", 1)) > 1 and int(lp["stop"]) > int(lp["start"]):
+        m.loop_start, m.loop_stop, m.loop_times, m.loop_plain = int(lp["start"]), int(lp["stop"]), int(lp["times"]), 1
+    elif lp and int(lp.get("times", 1)) < 1:
+        raise ValueError(f"config: loop.times {lp.get('times')}")
+    m.norm_eps = float(_req(_req(cfg, "norm", "the model"), "eps", "norm"))
+    m.norm_kind, m.norm_place = _seq.NORM_VECTOR, _seq.NORMS_FRONT
+    m.streams = int(_req(cfg, "streams", "the model"))
+    if m.streams < 1:
+        raise ValueError(f"config: streams {m.streams}")
+    m.logit_scale = 1.0
+    m.mode, m.max_tokens, m.max_seqs = mode, int(max_tokens), int(max_seqs)
+    return m, layers
+
+
+@register("Zopipel")
+def _load_zopipel(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seqs: int):
+    mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
+    desc, layers = zopipel_descs(cfg, mode, max_tokens, max_seqs)
     return _seq.SeqModel(desc, layers).load(weights)
 
 

@@ -14,10 +14,11 @@ BF16, F32 = 0, 1
 MIXER_ATTENTION, MIXER_WKV, MIXER_GLA, MIXER_HGRN2, MIXER_LATENT = 0, 1, 2, 3, 4
 ACT_RELU, ACT_SILU, ACT_GELU_TANH, ACT_XIELU = 0, 1, 2, 3
 FF_GLU, FF_POLYNORM, FF_EXPERTS, FF_DENSE = 0, 1, 2, 3
-NORM_SCALAR, NORM_ONE_PLUS = 0, 1
+NORM_SCALAR, NORM_ONE_PLUS, NORM_VECTOR = 0, 1, 2
+SINK_NONE, SINK_LEARNED, SINK_ZERO = 0, 1, 2
 ROUTE_SOFTMAX_ALL, ROUTE_TOP_LOGITS = 0, 1
 QK_NORM_NONE, QK_NORM_HEAD, QK_NORM_WHOLE = 0, 1, 2
-NORMS_AROUND, NORMS_BEHIND = 0, 1
+NORMS_AROUND, NORMS_BEHIND, NORMS_FRONT = 0, 1, 2
 
 
 class SeqError(RuntimeError):
@@ -33,7 +34,9 @@ class LayerDesc(C.Structure):
                 ("sink", C.c_int32), ("ff_kind", C.c_int32), ("experts", C.c_int32), ("identity", C.c_int32), ("top", C.c_int32),
                 ("groups", C.c_int32), ("groups_keep", C.c_int32), ("shared_ff", C.c_int32), ("res_gate", C.c_int32),
                 ("softcap", C.c_float), ("talk", C.c_int32), ("keep_first", C.c_int32), ("route_kind", C.c_int32),
-                ("shared_plain", C.c_int32), ("conv_taps", C.c_int32), ("layer_scale", C.c_int32)]
+                ("shared_plain", C.c_int32), ("conv_taps", C.c_int32), ("layer_scale", C.c_int32), ("conv_ff", C.c_int32),
+                ("rot_half", C.c_int32), ("rot_linear", C.c_float), ("proj_bias", C.c_int32), ("v_norm", C.c_int32),
+                ("head_temp", C.c_int32), ("q_rank", C.c_int32)]
 
     def __init__(self, *a, **kw):
         super().__init__(*a, **kw)
@@ -46,7 +49,7 @@ class ModelDesc(C.Structure):
                 ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("norm_eps", C.c_float), ("logit_scale", C.c_float),
                 ("mode", C.c_int32), ("max_tokens", C.c_int32), ("max_seqs", C.c_int32), ("norm_kind", C.c_int32),
                 ("logit_softcap", C.c_float), ("side_dim", C.c_int32), ("norm_place", C.c_int32), ("pos_base", C.c_float),
-                ("tied_head", C.c_int32)]
+                ("tied_head", C.c_int32), ("loop_plain", C.c_int32), ("streams", C.c_int32)]
 
 
 _i32 = C.POINTER(C.c_int32)
