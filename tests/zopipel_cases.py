@@ -96,7 +96,7 @@ def plant_pair(cfg, W, a, b, gain=12.0):
     positions: both get a large embedding along one coordinate of their own that no other token uses; the convolution passes these
     two coordinates unchanged; the query of head 0 reads b's coordinate and the key of its key/value head reads a's coordinate with
     the same vector r, placed on coordinates that are NOT rotated (attention: the ones behind rot.dims; latent attention: the plain
-    part of the head, reached through entry 0 of the two low-rank vectors)."""
+    part of the head, reached through entry 0 of the two low-rank vectors; the head's output gate is opened for b)."""
     W = {k: np.array(v, np.float32, copy=True) for k, v in W.items()}
     L = cfg["layers"][0]
     mx = L["mixer"]
@@ -131,4 +131,5 @@ def plant_pair(cfg, W, a, b, gain=12.0):
         W["l0.mix.dkv.norm"][0] = 1.0
         W["l0.mix.uq"][:d, 0] = r
         W["l0.mix.uk"][:d, 0] = r
+        W["l0.mix.g"][0, u] = 0.5   # head 0's gate is open at b
     return {k: to_bf16_values(x) for k, x in W.items()}
