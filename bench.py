@@ -280,17 +280,18 @@ def main():
     ap.add_argument("--arch-compare", default=None, choices=["w1024", "w2048", "w4096"],
                     help="instead of the headline workload: prompt and decode throughput of a Binusun-style model (layered sequence engine, bf16) "
                          "next to the INT4 Llama-style decoder at equal width, depth and feed-forward size; random weights")
-    ap.add_argument("--arch", default="Binusun", choices=["Binusun", "Tudasun", "Gulazen"],
+    ap.add_argument("--arch", default="Binusun", choices=["Binusun", "Tudasun", "Gulazen", "Zopipel"],
                     help="with --arch-compare: the design that is measured.  Tudasun (gated linear recurrences, latent attention, routed experts; bf16) "
                          "is put next to the Binusun hybrid on the same engine at equal width and depth; Gulazen (capped head-mixed window attention "
-                         "behind a short convolution, xIELU / routed feed-forward; bf16) next to seven Binusun attention layers of the same sizes")
+                         "behind a short convolution, xIELU / routed feed-forward; bf16) and Zopipel (hyper-connections, attention with a zero sink and "
+                         "windowed latent attention behind short convolutions; bf16) next to seven Binusun attention layers of the same sizes")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate depth (the number is then NOT a bench value)")
     args = ap.parse_args()
 
     if args.arch_compare:
         from turboinfer_b200 import bench_seq
-        if args.arch in ("Tudasun", "Gulazen"):
-            fn = bench_seq.compare_tudasun if args.arch == "Tudasun" else bench_seq.compare_gulazen
+        if args.arch in ("Tudasun", "Gulazen", "Zopipel"):
+            fn = {"Tudasun": bench_seq.compare_tudasun, "Gulazen": bench_seq.compare_gulazen, "Zopipel": bench_seq.compare_zopipel}[args.arch]
             res = fn(args.arch_compare, steps=max(1, args.steps), warmup=max(3, args.warmup))
             print(json.dumps({"metric": "arch_compare_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": max(1, args.steps), "warmup": max(3, args.warmup),
                               "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_GBps": measured_peak_gbs()}, **res}))

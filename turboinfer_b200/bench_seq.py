@@ -73,10 +73,29 @@ def binusun_attention_config_for(size: str) -> dict:
     return {"architecture": "Binusun", "layers": [cfg["layers"][1]] * 7, "norm": cfg["norm"], "logit_scale": 1.0, "vocab": cfg["vocab"], "width": cfg["width"]}
 
 
+def zopipel_config_for(size: str) -> dict:
+    """Five layers, attention / latent attention in turn, the middle two run twice: 7 layer runs (4 attention, 3 latent attention), all
+    with a gated gelu feed-forward of the size's inner width behind a four-tap convolution, four residual streams.  Attention: the
+    size's heads over all earlier tokens, every coordinate turning; latent attention: a cached row of 256 + 64, queries through a
+    vector of 3/8 of the width, the size's window."""
+    z = SIZES[size]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                     "rot": {"base": 10000.0, "dims": z["dim"], "scaling": {"factor": 2.0}}, "scale": 1.0 / math.sqrt(z["dim"])}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": z["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 256, "q_rank": 3 * z["width"] // 8, "mask": {"size": z["window"]},
+                     "rot": {"base": 500000.0, "dims": 64}, "scale": 1.0 / math.sqrt(192.0)}}
+    return {"architecture": "Zopipel", "canon": {"taps": 4}, "layers": [att, lat, att, lat, att], "loop": {"start": 1, "stop": 3, "times": 2},
+            "norm": {"eps": 1e-6}, "streams": 4, "vocab": z["vocab"], "width": z["width"]}
+
+
 def build_synthetic(cfg: dict, rank: int, dtype: str, max_tokens: int, max_seqs: int) -> seq.SeqModel:
     mode = {"bfloat16": seq.BF16, "float32": seq.F32}[dtype]
     if cfg["architecture"] == "Gulazen":
         desc, layers = models.gulazen_descs(cfg, mode, max_tokens, max_seqs)
+    elif cfg["architecture"] == "Zopipel":
+        desc, layers = models.zopipel_descs(cfg, mode, max_tokens, max_seqs)
     elif cfg["architecture"] == "Tudasun":
         shapes = {f"l{i}.mix.a1": (rank, cfg["width"]) for i, L in enumerate(cfg["layers"]) if L["type"] == "gla"}
         shapes.update({f"l{i}.rg1": (cfg["width"], cfg["width"]) for i in range(len(cfg["layers"]))})
@@ -89,6 +108,16 @@ def build_synthetic(cfg: dict, rank: int, dtype: str, max_tokens: int, max_seqs:
         leaf = name.split(".")[-1]
         if cfg["architecture"] in ("Tudasun", "Gulazen") and (leaf in ("norm1", "norm1b", "norm2", "norm2b", "b", "correction") or name == "final.norm"):
             amp, off = 0.1, (1.0 if name.endswith("a2.b") else 0.0)   # gains stored around zero, biases, router corrections
+        elif cfg["architecture"] == "Zopipel" and (leaf in ("norm1", "norm2", "temp") or name == "final.norm" or name.endswith(("dq.norm", "dkv.norm"))):
+            amp, off = 0.25, 1.0   # plain gains and per-head score factors around one
+        elif cfg["architecture"] == "Zopipel" and leaf == "b":
+            amp, off = 0.1, 0.0
+        elif leaf in ("in", "out") and ".hc" in name:
+            amp, off = 0.2, 0.6
+        elif leaf == "mix" and ".hc" in name:
+            amp, off = 0.15, 1.0 / shape[-1]
+        elif leaf == "canon2":
+            amp, off = 0.2, 0.0
         elif leaf in ("ls1", "ls2"):
             amp, off = 0.25, 0.5
         elif leaf == "canon1":
@@ -124,7 +153,8 @@ def prompt(n: int, vocab: int, offset: int = 0):
 
 
 def measure_seq(size: str, dtype: str, n_prompt: int, n_new: int, batch: int, steps: int, warmup: int, design: str = "Binusun") -> dict:
-    cfg = {"Tudasun": tudasun_config_for, "Gulazen": gulazen_config_for, "BinusunAttention": binusun_attention_config_for}.get(design, config_for)(size)
+    cfg = {"Tudasun": tudasun_config_for, "Gulazen": gulazen_config_for, "BinusunAttention": binusun_attention_config_for,
+           "Zopipel": zopipel_config_for}.get(design, config_for)(size)
     m = build_synthetic(cfg, SIZES[size]["rank"], dtype, max_tokens=(n_prompt + n_new + 64) * max(batch, 1) + 64, max_seqs=max(batch, 1))
     V = cfg["vocab"]
     launches0 = seq.launch_count()
@@ -205,6 +235,15 @@ def compare_gulazen(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_
     """Gulazen next to the closest model of the library, seven Binusun attention layers on the same engine (bf16 weights both)."""
     out = {"size": size, "shape": SIZES[size], "prompt_tokens": n_prompt, "decode_steps": n_new}
     for design, key in (("Gulazen", "gulazen_bf16"), ("BinusunAttention", "binusun_attention_bf16")):
+        out[key] = measure_seq(size, "bfloat16", n_prompt, n_new, 1, steps, warmup, design)
+        out[key + "_batch4"] = {k: v for k, v in measure_seq(size, "bfloat16", 256, n_new, 4, 1, 1, design).items() if k.startswith("decode") or k == "batch"}
+    return out
+
+
+def compare_zopipel(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_new: int = 64) -> dict:
+    """Zopipel next to the closest model of the library, seven Binusun attention layers on the same engine (bf16 weights both)."""
+    out = {"size": size, "shape": SIZES[size], "prompt_tokens": n_prompt, "decode_steps": n_new}
+    for design, key in (("Zopipel", "zopipel_bf16"), ("BinusunAttention", "binusun_attention_bf16")):
         out[key] = measure_seq(size, "bfloat16", n_prompt, n_new, 1, steps, warmup, design)
         out[key + "_batch4"] = {k: v for k, v in measure_seq(size, "bfloat16", 256, n_new, 4, 1, 1, design).items() if k.startswith("decode") or k == "batch"}
     return out

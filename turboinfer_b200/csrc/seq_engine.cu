@@ -709,8 +709,8 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         return 0;
     }
     dim3 grid((N + 63) / 64, (M + 63) / 64);
-    if (m.d.mode == TI_SEQ_BF16) gemm_bf16_kernel<<<grid, 128, 0, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, beta);
-    else gemm_f32_kernel<<<grid, 256, 0, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, beta);
+    if (m.d.mode == TI_SEQ_BF16) gemm_bf16_kernel<<<grid, 128, 0, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, beta, 0, 0, 0);
+    else gemm_f32_kernel<<<grid, 256, 0, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, beta, 0, 0, 0);
     LAUNCHED();
     return 0;
 }
@@ -724,6 +724,16 @@ int gemm_heads(Model& m, const float* A, int lda, int a_stride, const void* W, f
             TRY(launch_dep(gemv_heads_rows_kernel<__nv_bfloat16>, grid, dim3(kRowGemvThreads), (size_t)M * K * sizeof(float), A, lda, a_stride, (const __nv_bfloat16*)W, C, ldc, c_stride, M, N, K));
         else
             TRY(launch_dep(gemv_heads_rows_kernel<float>, grid, dim3(kRowGemvThreads), (size_t)M * K * sizeof(float), A, lda, a_stride, (const float*)W, C, ldc, c_stride, M, N, K));
+        LAUNCHED();
+        return 0;
+    }
+    // many rows: all heads in one launch of the tile kernels (a head's product is too small to fill the GPU by itself)
+    const dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
+    if (heads <= 65535 && grid.y <= 65535) {
+        if (m.d.mode == TI_SEQ_BF16)
+            gemm_bf16_kernel<<<grid, 128, 0, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, EPI_NONE, 1.f, 0.f, (size_t)a_stride, (size_t)N * K, (size_t)c_stride);
+        else
+            gemm_f32_kernel<<<grid, 256, 0, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, EPI_NONE, 1.f, 0.f, (size_t)a_stride, (size_t)N * K, (size_t)c_stride);
         LAUNCHED();
         return 0;
     }
@@ -963,12 +973,15 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     // norms in front only: sublayer `q` (0: mixer, 1: feed-forward) of layer run `ri` ends with its result in m.mo -- every stream is
     // rewritten, and the input of the sublayer that follows (the same run's feed-forward or the next run's mixer) goes to m.h; the last
     // sublayer of a run leaves the sum of the streams in m.x.  q < 0: nothing ends, the first sublayer of the step is opened.
+    bool all_single = true;   // a decoding step: every entry brings one row, and a sublayer's convolution reads its slot's state only
+    for (int e = 0; e < E; ++e) all_single = all_single && counts[e] == 1;
     auto hyper = [&](size_t ri, int q) -> int {
         const LayerW& L = m.layers[m.runs[ri].layer];
         HyperArgs a{};
         a.X = m.xs.p; a.S = m.n_streams; a.D = D; a.gvec = gv; a.eps = eps; a.h = m.h.p;
         const LayerW* next = nullptr;
         int nq = 0;
+        size_t nri = ri;
         if (q < 0) next = &L;
         else {
             a.y = m.mo.p; a.mix = L.hc_mix[q]; a.out = L.hc_out[q];
@@ -976,11 +989,24 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             if (q == 0 && L.d.ff > 0) { next = &L; nq = 1; }
             else {
                 a.sum = m.x.p;
-                if (ri + 1 < m.runs.size()) next = &m.layers[m.runs[ri + 1].layer];
+                if (ri + 1 < m.runs.size()) { nri = ri + 1; next = &m.layers[m.runs[nri].layer]; }
             }
         }
-        if (next) { a.in_next = next->hc_in[nq]; a.gain = nq == 0 ? next->norm1 : next->norm2; }
-        TRY(launch_dep(hyper_kernel, dim3(T), dim3(nt), 0, a));
+        if (next) {
+            a.in_next = next->hc_in[nq]; a.gain = nq == 0 ? next->norm1 : next->norm2;
+            const float* cw = nq == 0 ? next->canon : next->canon2;
+            if (all_single && cw) {   // the next sublayer's convolution rides along
+                a.conv_w = cw; a.conv_state = nq == 0 ? m.runs[nri].conv_state.p : m.runs[nri].conv_state2.p; a.hc = m.hc.p; a.taps = next->d.conv_taps;
+            }
+        }
+        const bool few = T <= 2 * g_num_sms;   // few rows: more threads a row
+#define TI_HYPER_CASE(N) \
+    case N: TRY(launch_dep(hyper_kernel<N>, dim3(T), dim3(few ? std::min(hyper_max_threads<N>(), std::max(nt, (D + 31) / 32 * 32)) : nt), 0, a, sm)); break;
+        switch (m.n_streams) {
+            TI_HYPER_CASE(1) TI_HYPER_CASE(2) TI_HYPER_CASE(3) TI_HYPER_CASE(4) TI_HYPER_CASE(5) TI_HYPER_CASE(6) TI_HYPER_CASE(7) TI_HYPER_CASE(8)
+            default: TRY(launch_dep(hyper_kernel<0>, dim3(T), dim3(nt), 0, a, sm)); break;
+        }
+#undef TI_HYPER_CASE
         LAUNCHED();
         return 0;
     };
@@ -1006,10 +1032,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && s.vdim <= 512 && tsmem <= g_smem_optin && (s.v_ld % 4 == 0);
         // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
         const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
-                           (s.kv_heads * s.dim) % 4 == 0 && !s.sink && s.v_ld == 0;
+                           (s.kv_heads * s.dim) % 4 == 0 && s.v_ld == 0;
         // bf16 mode, a shared key/value head with the values inside the key rows (latent attention), instantiated sizes: tensor cores
         const bool lat_size = (s.dim == 320 && s.vdim == 256) || (s.dim == 192 && s.vdim == 128) || (s.dim == 160 && s.vdim == 128);
-        const bool lat_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles > 0 && v_in_k && s.window == 0 && !s.out_gate && !s.qk_norm && lat_size;
+        const bool lat_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles > 0 && v_in_k && (!s.out_gate || s.gate) && !s.qk_norm && lat_size;
         const int* rest = (tiled_ok || h3_ok || lat_ok) ? d_small : nullptr;
         const int n_rest = (tiled_ok || h3_ok || lat_ok) ? n_small : T;
         if (lat_ok) {
@@ -1139,8 +1165,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             LAUNCHED();
         }
         const float* mix_in = behind ? m.x.p : m.h.p;   // what the mixer reads
-        if (L.d.conv_taps >= 1) {   // ... with the short convolution over the sequence's last inputs added
-            TRY(short_conv(mix_in, L.canon, L.d.conv_taps, R.conv_state.p, m.hc.p));
+        if (L.d.conv_taps >= 1) {   // ... with the short convolution over the sequence's last inputs added (decoding with norms in front: done already)
+            if (!(front && all_single)) TRY(short_conv(mix_in, L.canon, L.d.conv_taps, R.conv_state.p, m.hc.p));
             mix_in = m.hc.p;
         }
         const float* front_in = fuse_front ? m.x.p : mix_in;
@@ -1290,7 +1316,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             else TRY(post(L.norm1b, gv, (fuse_ff || behind) ? nullptr : L.norm2, gate1, gate1_ld, L.rg1b, nullptr));
             const float* ff_in = behind ? m.x.p : m.h.p;   // what the feed-forward reads
             if (L.canon2) {
-                TRY(short_conv(ff_in, L.canon2, L.d.conv_taps, R.conv_state2.p, m.hc.p));
+                if (!(front && all_single)) TRY(short_conv(ff_in, L.canon2, L.d.conv_taps, R.conv_state2.p, m.hc.p));
                 ff_in = m.hc.p;
             }
             const float* gate2 = nullptr;

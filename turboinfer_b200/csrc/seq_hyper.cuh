@@ -27,14 +27,27 @@ struct HyperArgs {
     float* sum;             // [T][D] or null: sum of the streams after the update
     int S, D, gvec;
     float eps;
+    // a step whose entries all bring ONE row (decoding): the next sublayer's short convolution h + conv(h) rides along -- it reads
+    // the slot's state only -- and the slot's state is shifted here (the layout of short_conv_kernel); null: the step runs that kernel
+    const float* conv_w;    // [D][taps]
+    float* conv_state;      // [slots][taps - 1][D]
+    float* hc;              // [T][D]
+    int taps;
 };
 
-__global__ void __launch_bounds__(256) hyper_kernel(HyperArgs a) {
+// NS > 0: the number of streams, known when the kernel is compiled (the copies of a coordinate live in registers);
+// NS = 0: any number up to kMaxStreams (small arrays indexed at run time).
+// A step of few rows is a handful of blocks whose time is the latency of their loads, one after the other: it is launched with as many
+// threads a row as the registers allow (hyper_max_threads), so that a thread meets one or two coordinates; many rows run 256 a row.
+template <int NS> constexpr int hyper_max_threads() { return NS == 0 ? 256 : NS <= 4 ? 1024 : 512; }
+template <int NS>
+__global__ void __launch_bounds__(hyper_max_threads<NS>()) hyper_kernel(HyperArgs a, StepMeta m) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
+    constexpr int CAP = NS > 0 ? NS : kMaxStreams;
     __shared__ float red[32];
     __shared__ float s_mix[kMaxStreams * kMaxStreams], s_out[kMaxStreams], s_in[kMaxStreams];
-    const int t = blockIdx.x, S = a.S, D = a.D;
+    const int t = blockIdx.x, S = NS > 0 ? NS : a.S, D = a.D;
     if (a.y)
         for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = a.mix[i];
     if (threadIdx.x < S) {
@@ -45,23 +58,24 @@ __global__ void __launch_bounds__(256) hyper_kernel(HyperArgs a) {
     float* xr = a.X + (size_t)t * S * D;
     float ss = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float x[kMaxStreams];
+        float x[CAP];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) x[s] = s < S ? xr[(size_t)s * D + d] : 0.f;
+        for (int s = 0; s < CAP; ++s)
+            if (s < S) x[s] = xr[(size_t)s * D + d];
         if (a.y) {
             const float yv = a.y[(size_t)t * D + d] + (a.bias ? a.bias[d] : 0.f);
-            float n[kMaxStreams];
+            float n[CAP];
 #pragma unroll
-            for (int to = 0; to < kMaxStreams; ++to) {
-                if (to >= S) continue;
-                float acc = 0.f;
+            for (int to = 0; to < CAP; ++to)
+                if (to < S) {
+                    float acc = 0.f;
 #pragma unroll
-                for (int s = 0; s < kMaxStreams; ++s)
-                    if (s < S) acc = fmaf(s_mix[s * S + to], x[s], acc);
-                n[to] = fmaf(s_out[to], yv, acc);
-            }
+                    for (int s = 0; s < CAP; ++s)
+                        if (s < S) acc = fmaf(s_mix[s * S + to], x[s], acc);
+                    n[to] = fmaf(s_out[to], yv, acc);
+                }
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
+            for (int s = 0; s < CAP; ++s)
                 if (s < S) {
                     x[s] = n[s];
                     xr[(size_t)s * D + d] = n[s];
@@ -70,14 +84,14 @@ __global__ void __launch_bounds__(256) hyper_kernel(HyperArgs a) {
         if (a.sum) {
             float tot = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
+            for (int s = 0; s < CAP; ++s)
                 if (s < S) tot += x[s];
             a.sum[(size_t)t * D + d] = tot;
         }
         if (a.in_next) {
             float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
+            for (int s = 0; s < CAP; ++s)
                 if (s < S) u = fmaf(s_in[s], x[s], u);
             a.h[(size_t)t * D + d] = u;   // (the thread that wrote it scales it below)
             ss += u * u;
@@ -86,7 +100,23 @@ __global__ void __launch_bounds__(256) hyper_kernel(HyperArgs a) {
     if (!a.in_next) return;
     ss = block_sum(ss, red);
     const float sc = 1.f / sqrtf(ss / (float)D + a.eps);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) a.h[(size_t)t * D + d] *= sc * a.gain[a.gvec ? d : 0];
+    if (!a.conv_w) {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) a.h[(size_t)t * D + d] *= sc * a.gain[a.gvec ? d : 0];
+        return;
+    }
+    const int e = m.row_ent[t], pos = m.ent_pos0[e], taps = a.taps;
+    float* st = a.conv_state + (size_t)m.ent_slot[e] * (taps - 1) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float hv = a.h[(size_t)t * D + d] * (sc * a.gain[a.gvec ? d : 0]);
+        float acc = fmaf(a.conv_w[(size_t)d * taps + taps - 1], hv, hv);
+        for (int j = 0; j + 1 < taps; ++j) {   // state entry j holds the input at position pos - (taps - 1) + j
+            const float v = pos - (taps - 1) + j >= 0 ? st[(size_t)j * D + d] : 0.f;
+            acc = fmaf(a.conv_w[(size_t)d * taps + j], v, acc);
+            if (j > 0) st[(size_t)(j - 1) * D + d] = v;
+        }
+        if (taps > 1) st[(size_t)(taps - 2) * D + d] = hv;
+        a.hc[(size_t)t * D + d] = acc;
+    }
 }
 
 }  // namespace seq

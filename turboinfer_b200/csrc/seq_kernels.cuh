@@ -172,9 +172,13 @@ __device__ __forceinline__ float epi_apply(float v, int epi, float alpha, float 
 }
 
 // true fp32: 64 x 64 tile, 16-deep k-steps, 256 threads with 4 x 4 outputs each
+// (grid.z > 1: a batch of products, number z reads A + z * za, W + z * zw and writes C + z * zc -- one small matrix per head)
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* A, int lda, const float* W, float* C, int ldc, int M, int N, int K,
-                                                        int epi, float alpha, float beta) {
+                                                        int epi, float alpha, float beta, size_t za, size_t zw, size_t zc) {
     __shared__ float As[16][64 + 4], Ws[16][64 + 4];
+    A += blockIdx.z * za;
+    W += blockIdx.z * zw;
+    C += blockIdx.z * zc;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
     float acc[4][4] = {};
@@ -216,10 +220,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+// (grid.z > 1: a batch of products, as in gemm_f32_kernel)
 __global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N,
-                                                         int K, int epi, float alpha, float beta) {
+                                                         int K, int epi, float alpha, float beta, size_t za, size_t zw, size_t zc) {
     constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;
     __shared__ __align__(16) __nv_bfloat16 As[BM * LD], Ws[BN * LD];
+    A += blockIdx.z * za;
+    W += blockIdx.z * zw;
+    C += blockIdx.z * zc;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;

@@ -6,8 +6,8 @@
 //     score_h(i, j) = (q_h . Uk_h c_j + qr_h . kr_j) * scale = ((Uk_h^T q_h) . c_j + qr_h . kr_j) * scale
 //     out_h(i)      = sum_j p_h(i, j) Uv_h c_j                = Uv_h (sum_j p_h(i, j) c_j)
 // so the attention itself is one key/value head of size rank + rot (values = the first rank coordinates of the key row) shared
-// by all query heads, and runs on the paged attention kernels of seq_kernels.cuh / seq_attn_tc.cuh (window 0, value pool = key
-// pool, sink term).  This file holds what is special: the cache append and the query's rotated part.
+// by all query heads, and runs on the paged attention kernels of seq_kernels.cuh / seq_attn_tc.cuh (value pool = key pool; a
+// sliding window, a sink term and a per-head output gate -- one number a head, so it commutes with Uv -- are the layer's choice).  This file holds what is special: the cache append and the query's rotated part.
 #pragma once
 #include "seq_attn_tc.cuh"
 #include "seq_kernels.cuh"
@@ -119,24 +119,26 @@ __global__ void __launch_bounds__(256, 1) latent_attention_h3_kernel(const float
     for (int n = 0; n < NTH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int last_pos = pos0 + M - 1;
-    const int warp_last = pos0 + min(16 * rg + 15, M - 1);
+    const int lo = (s.window > 0 && pos0 - s.window + 1 > 0) ? pos0 - s.window + 1 : 0;   // first key any row of the tile sees
+    const int warp_first = pos0 + 16 * rg, warp_last = pos0 + min(16 * rg + 15, M - 1);
+    const int warp_lo = (s.window > 0 && warp_first - s.window + 1 > 0) ? warp_first - s.window + 1 : 0;
     const uint32_t* qh_row = reinterpret_cast<const uint32_t*>(Qh + (16 * rg + g) * LD) + t;
     const uint32_t* ql_row = reinterpret_cast<const uint32_t*>(Ql + (16 * rg + g) * LD) + t;
     const int lm = lane >> 3, lr = lane & 7;
     const uint32_t k_ld = (uint32_t)(((lr + 8 * (lm >> 1)) * LD + 8 * (lm & 1)) * 2);
     const uint32_t v_ld = (uint32_t)(((lr + 8 * (lm & 1)) * LD + 8 * (lm >> 1)) * 2);
     const uint32_t kh_s = smem_u32(Kh), kl_s = smem_u32(Kl);
-    for (int t0 = 0; t0 <= last_pos; t0 += kTcKT) {   // a key tile = a page
+    for (int t0 = lo / kPageTokens * kPageTokens; t0 <= last_pos; t0 += kTcKT) {   // a key tile = a page; pages below the window are not visited
         __syncthreads();
         const size_t tok0 = (size_t)table[t0 / kPageTokens] * kPageTokens;
         for (int i = tid; i < kTcKT * (DK / 4); i += 256) {
             const int kk = i / (DK / 4), d4 = (i % (DK / 4)) * 4;
             float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t0 + kk <= last_pos) kv = *reinterpret_cast<const float4*>(pool + (tok0 + kk) * (size_t)DK + d4);
+            if (t0 + kk >= lo && t0 + kk <= last_pos) kv = *reinterpret_cast<const float4*>(pool + (tok0 + kk) * (size_t)DK + d4);
             store_split4(kv, Kh + kk * LD + d4, Kl + kk * LD + d4);
         }
         __syncthreads();
-        if (t0 > warp_last || 16 * rg >= M) continue;   // nothing of this page is visible to the warp's rows
+        if (t0 > warp_last || t0 + kTcKT - 1 < warp_lo || 16 * rg >= M) continue;   // nothing of this page is visible to the warp's rows
         float sc[kTcKT / 8][4];
 #pragma unroll
         for (int j = 0; j < kTcKT / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
@@ -159,14 +161,15 @@ __global__ void __launch_bounds__(256, 1) latent_attention_h3_kernel(const float
             }
         }
         const int qp0 = pos0 + r0, qp1 = pos0 + r1;
+        const int w = s.window > 0 ? s.window : 0x3FFFFFFF;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < kTcKT / 8; ++j) {
             const int key = t0 + 8 * j + 2 * t;
-            sc[j][0] = (key <= qp0 && r0 < M) ? sc[j][0] * s.scale : -INFINITY;
-            sc[j][1] = (key + 1 <= qp0 && r0 < M) ? sc[j][1] * s.scale : -INFINITY;
-            sc[j][2] = (key <= qp1 && r1 < M) ? sc[j][2] * s.scale : -INFINITY;
-            sc[j][3] = (key + 1 <= qp1 && r1 < M) ? sc[j][3] * s.scale : -INFINITY;
+            sc[j][0] = (key <= qp0 && key > qp0 - w && r0 < M) ? sc[j][0] * s.scale : -INFINITY;
+            sc[j][1] = (key + 1 <= qp0 && key + 1 > qp0 - w && r0 < M) ? sc[j][1] * s.scale : -INFINITY;
+            sc[j][2] = (key <= qp1 && key > qp1 - w && r1 < M) ? sc[j][2] * s.scale : -INFINITY;
+            sc[j][3] = (key + 1 <= qp1 && key + 1 > qp1 - w && r1 < M) ? sc[j][3] * s.scale : -INFINITY;
             mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
             mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
         }
@@ -219,7 +222,8 @@ __global__ void __launch_bounds__(256, 1) latent_attention_h3_kernel(const float
             }
         }
     }
-    const float i0 = r0 < M ? attn_finish_factor(s, h, m0, l0) : 0.f, i1 = r1 < M ? attn_finish_factor(s, h, m1, l1) : 0.f;
+    const float i0 = r0 < M ? attn_finish_factor(s, h, m0, l0) * attn_gate(s, q, row0 + r0, h) : 0.f;
+    const float i1 = r1 < M ? attn_finish_factor(s, h, m1, l1) * attn_gate(s, q, row0 + r1, h) : 0.f;
     const size_t opitch = (size_t)s.heads * DV;
 #pragma unroll
     for (int n = 0; n < NTH; ++n) {
