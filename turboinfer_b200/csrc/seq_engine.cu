@@ -999,12 +999,17 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 a.conv_w = cw; a.conv_state = nq == 0 ? m.runs[nri].conv_state.p : m.runs[nri].conv_state2.p; a.hc = m.hc.p; a.taps = next->d.conv_taps;
             }
         }
-        const bool few = T <= 2 * g_num_sms;   // few rows: more threads a row
-#define TI_HYPER_CASE(N) \
-    case N: TRY(launch_dep(hyper_kernel<N>, dim3(T), dim3(few ? std::min(hyper_max_threads<N>(), std::max(nt, (D + 31) / 32 * 32)) : nt), 0, a, sm)); break;
+        // few rows: more threads a row, one coordinate each; many rows: 256 threads with four neighbouring coordinates each (D in fours)
+        const bool few = T <= 2 * g_num_sms;
+        const bool v4 = !few && D % 4 == 0;
+#define TI_HYPER_CASE(N)                                                                                                                              \
+    case N:                                                                                                                                           \
+        if (v4) TRY(launch_dep(hyper_kernel<N, 4>, dim3(T), dim3(nt), 0, a, sm));                                                                     \
+        else TRY(launch_dep(hyper_kernel<N, 1>, dim3(T), dim3(few ? std::min(hyper_max_threads<N>(), std::max(nt, (D + 31) / 32 * 32)) : nt), 0, a, sm)); \
+        break;
         switch (m.n_streams) {
             TI_HYPER_CASE(1) TI_HYPER_CASE(2) TI_HYPER_CASE(3) TI_HYPER_CASE(4) TI_HYPER_CASE(5) TI_HYPER_CASE(6) TI_HYPER_CASE(7) TI_HYPER_CASE(8)
-            default: TRY(launch_dep(hyper_kernel<0>, dim3(T), dim3(nt), 0, a, sm)); break;
+            default: TRY(launch_dep(hyper_kernel<0, 1>, dim3(T), dim3(nt), 0, a, sm)); break;
         }
 #undef TI_HYPER_CASE
         LAUNCHED();
@@ -1012,7 +1017,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     };
     // the short convolution in front of a sublayer: y = x + conv(x) over the sequence's last inputs; the slot then keeps the newest ones
     auto short_conv = [&](const float* in, const float* w, int taps, float* state, float* out) -> int {
-        TRY(launch_dep(short_conv_kernel, dim3(T, T <= 64 ? (D + nt - 1) / nt : 1), dim3(nt), 0, in, sm, D, taps, w, state, out));
+        if (T > 64 && D % 4 == 0) TRY(launch_dep(short_conv_kernel<4>, dim3(T), dim3(std::min(nt, (D / 4 + 31) / 32 * 32)), 0, in, sm, D, taps, w, state, out));
+        else TRY(launch_dep(short_conv_kernel<1>, dim3(T, T <= 64 ? (D + nt - 1) / nt : 1), dim3(nt), 0, in, sm, D, taps, w, state, out));
         LAUNCHED();
         bool many = false;   // (an entry of one row has shifted its state in the kernel above)
         for (int e = 0; e < E; ++e) many = many || counts[e] > 1;

@@ -27,27 +27,63 @@ namespace seq {
 // for positions before 0 are never read (a slot that is used again needs no clearing).
 // An entry that brings ONE row (a decoded token) also shifts its slot's state here: the thread that read a coordinate's old entries
 // writes its new ones (short_conv_save_kernel then skips that entry).
+template <int V> __device__ __forceinline__ void conv_load(const float* p, float (&v)[V]) {
+    if constexpr (V == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+        v[0] = *p;
+    }
+}
+template <int V> __device__ __forceinline__ void conv_store(float* p, const float (&v)[V]) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else *p = v[0];
+}
+// V = 4: a thread takes four neighbouring coordinates with 16-byte loads and stores (D in whole fours); V = 1: one coordinate at a time.
+template <int V>
 __global__ void short_conv_kernel(const float* x, StepMeta m, int D, int taps, const float* w, float* state, float* y) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
+    constexpr int CH = V == 4 ? 4 : 8;   // taps whose inputs are requested together
     const int t = blockIdx.x, e = m.row_ent[t], i = t - m.ent_row0[e], pos0 = m.ent_pos0[e];
     float* st = state + (size_t)m.ent_slot[e] * (taps - 1) * D;
     const bool alone = m.ent_row0[e + 1] - m.ent_row0[e] == 1;
-    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
-        const float xv = x[(size_t)t * D + d];
-        float acc = xv;
-        for (int j = 0; j < taps; ++j) {
-            const int back = taps - 1 - j;
-            float v = 0.f;
-            if (back == 0) v = xv;
-            else if (i - back >= 0) v = x[(size_t)(t - back) * D + d];
-            else if (pos0 + i - back >= 0) v = st[(size_t)(taps - 1 + i - back) * D + d];
-            acc = fmaf(w[(size_t)d * taps + j], v, acc);
+    for (int d = (blockIdx.y * blockDim.x + threadIdx.x) * V; d < D; d += gridDim.y * blockDim.x * V) {
+        float xv[V], acc[V];
+        conv_load<V>(x + (size_t)t * D + d, xv);
+#pragma unroll
+        for (int c = 0; c < V; ++c) acc[c] = xv[c];
+        // the taps' inputs are requested together (CH at a time), then multiplied in ascending order of the tap
+        for (int j0 = 0; j0 < taps; j0 += CH) {
+            float v[CH][V], wv[CH][V];
+#pragma unroll
+            for (int q = 0; q < CH; ++q) {
+                const int j = j0 + q, back = taps - 1 - j;
+                const bool in_step = i - back >= 0;
+                const bool ok = j < taps && (in_step || pos0 + i - back >= 0);
+                const float* src = in_step ? x + (size_t)(t - back) * D + d : st + (size_t)(taps - 1 + i - back) * D + d;
+                if (ok) conv_load<V>(src, v[q]);
+#pragma unroll
+                for (int c = 0; c < V; ++c) {
+                    if (!ok) v[q][c] = 0.f;
+                    wv[q][c] = j < taps ? w[(size_t)(d + c) * taps + j] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < CH; ++q)
+                if (j0 + q < taps) {
+#pragma unroll
+                    for (int c = 0; c < V; ++c) acc[c] = fmaf(wv[q][c], v[q][c], acc[c]);
+                }
         }
-        y[(size_t)t * D + d] = acc;
+        conv_store<V>(y + (size_t)t * D + d, acc);
         if (alone) {
-            for (int s = 0; s + 2 < taps; ++s) st[(size_t)s * D + d] = st[(size_t)(s + 1) * D + d];
-            if (taps > 1) st[(size_t)(taps - 2) * D + d] = xv;
+            for (int s = 0; s + 2 < taps; ++s) {
+                float o[V];
+                conv_load<V>(st + (size_t)(s + 1) * D + d, o);
+                conv_store<V>(st + (size_t)s * D + d, o);
+            }
+            if (taps > 1) conv_store<V>(st + (size_t)(taps - 2) * D + d, xv);
         }
     }
 }
