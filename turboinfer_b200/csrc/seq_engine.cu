@@ -1017,7 +1017,11 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     };
     // the short convolution in front of a sublayer: y = x + conv(x) over the sequence's last inputs; the slot then keeps the newest ones
     auto short_conv = [&](const float* in, const float* w, int taps, float* state, float* out) -> int {
-        if (T > 64 && D % 4 == 0) TRY(launch_dep(short_conv_kernel<4>, dim3(T), dim3(std::min(nt, (D / 4 + 31) / 32 * 32)), 0, in, sm, D, taps, w, state, out));
+        constexpr int kConvRows = 8;   // rows a block of the many-rows kernel takes
+        const dim3 rows_grid((T + kConvRows - 1) / kConvRows, (D / 4 + 127) / 128);
+        if (T > 64 && D % 4 == 0 && taps <= 4) TRY(launch_dep(short_conv_rows_kernel<kConvRows, 4>, rows_grid, dim3(128), 0, in, sm, T, D, taps, w, state, out));
+        else if (T > 64 && D % 4 == 0 && taps <= 8) TRY(launch_dep(short_conv_rows_kernel<kConvRows, 8>, rows_grid, dim3(128), 0, in, sm, T, D, taps, w, state, out));
+        else if (T > 64 && D % 4 == 0) TRY(launch_dep(short_conv_kernel<4>, dim3(T), dim3(std::min(nt, (D / 4 + 31) / 32 * 32)), 0, in, sm, D, taps, w, state, out));
         else TRY(launch_dep(short_conv_kernel<1>, dim3(T, T <= 64 ? (D + nt - 1) / nt : 1), dim3(nt), 0, in, sm, D, taps, w, state, out));
         LAUNCHED();
         bool many = false;   // (an entry of one row has shifted its state in the kernel above)

@@ -87,6 +87,55 @@ __global__ void short_conv_kernel(const float* x, StepMeta m, int D, int taps, c
         }
     }
 }
+// Many rows (prompt portions): a block takes R consecutive rows and a thread four neighbouring coordinates (D in whole fours), whose
+// weights (taps <= KT) it reads ONCE and keeps in registers; the earlier rows' inputs were read by the same block a row before (L1).
+// The arithmetic of a coordinate is that of short_conv_kernel: acc = x, then the taps in ascending order.
+template <int R, int KT>
+__global__ void __launch_bounds__(128) short_conv_rows_kernel(const float* x, StepMeta m, int T, int D, int taps, const float* w, float* state, float* y) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    const int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (d >= D) return;
+    float wv[KT][4];
+#pragma unroll
+    for (int j = 0; j < KT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) wv[j][c] = j < taps ? w[(size_t)(d + c) * taps + j] : 0.f;
+    const int t0 = blockIdx.x * R, t1 = min(T, t0 + R);
+    for (int t = t0; t < t1; ++t) {
+        const int e = m.row_ent[t], i = t - m.ent_row0[e], pos0 = m.ent_pos0[e];
+        float* st = state + (size_t)m.ent_slot[e] * (taps - 1) * D;
+        const bool alone = m.ent_row0[e + 1] - m.ent_row0[e] == 1;
+        float xv[4], acc[4], v[KT][4];
+        conv_load<4>(x + (size_t)t * D + d, xv);
+#pragma unroll
+        for (int j = 0; j < KT; ++j) {
+            const int back = taps - 1 - j;
+            const bool in_step = i - back >= 0;
+            const bool ok = j < taps && (in_step || pos0 + i - back >= 0);
+            const float* src = in_step ? x + (size_t)(t - back) * D + d : st + (size_t)(taps - 1 + i - back) * D + d;
+            if (ok) conv_load<4>(src, v[j]);
+            else v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[c] = xv[c];
+#pragma unroll
+        for (int j = 0; j < KT; ++j)
+            if (j < taps) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[c] = fmaf(wv[j][c], v[j][c], acc[c]);
+            }
+        conv_store<4>(y + (size_t)t * D + d, acc);
+        if (alone) {
+            for (int s = 0; s + 2 < taps; ++s) {
+                float o[4];
+                conv_load<4>(st + (size_t)(s + 1) * D + d, o);
+                conv_store<4>(st + (size_t)s * D + d, o);
+            }
+            if (taps > 1) conv_store<4>(st + (size_t)(taps - 2) * D + d, xv);
+        }
+    }
+}
 // after all rows of the step have read the old state: the slot keeps the last taps - 1 inputs of its sequence
 __global__ void short_conv_save_kernel(const float* x, StepMeta m, int D, int taps, float* state) {
     pdl_launch_dependents();
