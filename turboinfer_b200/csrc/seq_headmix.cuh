@@ -88,20 +88,48 @@ __global__ void short_conv_kernel(const float* x, StepMeta m, int D, int taps, c
     }
 }
 // Many rows (prompt portions): a block takes R consecutive rows and a thread four neighbouring coordinates (D in whole fours), whose
-// weights (taps <= KT) it reads ONCE and keeps in registers; the earlier rows' inputs were read by the same block a row before (L1).
-// The arithmetic of a coordinate is that of short_conv_kernel: acc = x, then the taps in ascending order.
+// weights (taps <= KT) it reads ONCE and keeps in registers, the tap that reaches `back` rows back in entry KT - 1 - back.
+// Rows that all lie in one entry, taps - 1 rows or more behind its first: their inputs and those of the taps - 1 rows in front are
+// requested together, each once (no state is read or shifted).  Other blocks (an entry's first rows, entries of few rows) go row by
+// row.  The arithmetic of a coordinate is that of short_conv_kernel either way: acc = x, then the taps from the oldest input on.
 template <int R, int KT>
-__global__ void __launch_bounds__(128) short_conv_rows_kernel(const float* x, StepMeta m, int T, int D, int taps, const float* w, float* state, float* y) {
+__global__ void __launch_bounds__(128) short_conv_rows_kernel(const float* __restrict__ x, StepMeta m, int T, int D, int taps, const float* __restrict__ w, float* state, float* __restrict__ y) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (d >= D) return;
+    const int skip = KT - taps;   // entries below it hold no tap
     float wv[KT][4];
 #pragma unroll
-    for (int j = 0; j < KT; ++j)
+    for (int q = 0; q < KT; ++q)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) wv[j][c] = j < taps ? w[(size_t)(d + c) * taps + j] : 0.f;
+        for (int c = 0; c < 4; ++c) wv[q][c] = q >= skip ? w[(size_t)(d + c) * taps + q - skip] : 0.f;
     const int t0 = blockIdx.x * R, t1 = min(T, t0 + R);
+    const int e0 = m.row_ent[t0];
+    if (e0 == m.row_ent[t1 - 1] && t0 - m.ent_row0[e0] >= taps - 1) {
+        float xs[R + KT - 1][4];   // rows t0 - (KT - 1) .. t0 + R - 1
+#pragma unroll
+        for (int r = 0; r < R + KT - 1; ++r) {
+            const int t = t0 - (KT - 1) + r;
+            if (r >= skip && t < t1) conv_load<4>(x + (size_t)t * D + d, xs[r]);
+            else xs[r][0] = xs[r][1] = xs[r][2] = xs[r][3] = 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            if (t0 + r < t1) {
+                float acc[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[c] = xs[r + KT - 1][c];
+#pragma unroll
+                for (int q = 0; q < KT; ++q)
+                    if (q >= skip) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[c] = fmaf(wv[q][c], xs[r + q][c], acc[c]);
+                    }
+                conv_store<4>(y + (size_t)(t0 + r) * D + d, acc);
+            }
+        return;
+    }
     for (int t = t0; t < t1; ++t) {
         const int e = m.row_ent[t], i = t - m.ent_row0[e], pos0 = m.ent_pos0[e];
         float* st = state + (size_t)m.ent_slot[e] * (taps - 1) * D;
@@ -109,21 +137,21 @@ __global__ void __launch_bounds__(128) short_conv_rows_kernel(const float* x, St
         float xv[4], acc[4], v[KT][4];
         conv_load<4>(x + (size_t)t * D + d, xv);
 #pragma unroll
-        for (int j = 0; j < KT; ++j) {
-            const int back = taps - 1 - j;
+        for (int q = 0; q < KT; ++q) {
+            const int back = KT - 1 - q;
             const bool in_step = i - back >= 0;
-            const bool ok = j < taps && (in_step || pos0 + i - back >= 0);
+            const bool ok = q >= skip && (in_step || pos0 + i - back >= 0);
             const float* src = in_step ? x + (size_t)(t - back) * D + d : st + (size_t)(taps - 1 + i - back) * D + d;
-            if (ok) conv_load<4>(src, v[j]);
-            else v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
+            if (ok) conv_load<4>(src, v[q]);
+            else v[q][0] = v[q][1] = v[q][2] = v[q][3] = 0.f;
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[c] = xv[c];
 #pragma unroll
-        for (int j = 0; j < KT; ++j)
-            if (j < taps) {
+        for (int q = 0; q < KT; ++q)
+            if (q >= skip) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) acc[c] = fmaf(wv[j][c], v[j][c], acc[c]);
+                for (int c = 0; c < 4; ++c) acc[c] = fmaf(wv[q][c], v[q][c], acc[c]);
             }
         conv_store<4>(y + (size_t)t * D + d, acc);
         if (alone) {
