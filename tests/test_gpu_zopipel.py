@@ -40,6 +40,8 @@ MECHANISMS = {
     "latent_with_ff": make_config([latent(mlp=dense(56))]),
     "one_stream": make_config([attn(mlp=dense(24)), latent()], streams=1),
     "five_streams": make_config([latent(mlp=dense(24)), attn()], streams=5),
+    "nine_streams": make_config([attn(mlp=dense(24)), latent(mlp=dense(16))], streams=9),
+    "nine_taps": make_config([latent(mlp=dense(24)), attn(mlp=dense(16))], taps=9),
     "one_tap": make_config([attn(mlp=dense(24)), latent(mlp=dense(8))], taps=1),
     "two_taps_odd_width": make_config([attn(heads=3, kv_heads=3, dim=10, vdim=7, rot_dims=6), latent(heads=5, dim=6, rot_dim=2, vdim=5, kv_rank=9, q_rank=7)],
                                       width=37, taps=2, eps=1e-3),
@@ -106,6 +108,22 @@ def test_prefill_equals_token_by_token(dtype):
     check_logits(a, want, dtype)
     check_logits(b, want, dtype)
     check_logits(b, a, dtype)
+
+
+def test_many_streams_and_taps_token_by_token():
+    """More streams than the stream kernel keeps with a compile-time count, more taps than the prompt convolution keeps in
+    registers: a prompt in one step, in portions, and token by token (the decode rows' convolution rides in the stream kernel)."""
+    cfg = make_config([attn(mlp=dense(24)), latent(window=13, mlp=dense(16))], taps=9, streams=9, loop=(0, 2, 2))
+    W = random_weights(cfg, seed=15, canon_amp=1.0)
+    toks = tokens(90, cfg["vocab"], 4)
+    want, _ = plain.run(cfg, W, toks)
+    m = build_engine(cfg, W, "float32")
+    a = whole(m, toks)
+    b = run_schedule(m, {"a": toks}, [[("a", 1)] for _ in toks])["a"]
+    c = run_schedule(m, {"a": toks}, [[("a", n)] for n in (70, 2, 1, 1, 5, 1, 10)])["a"]
+    m.free()
+    for got in (a, b, c):
+        check_logits(got, want, "float32")
 
 
 @pytest.mark.parametrize("sizes", [[2] * 40, [3, 61, 2, 64, 5, 65, 1, 63, 2], [64, 64, 64], [1, 127, 2, 2, 100], [129, 2, 33], [7, 1, 1, 8, 9, 1, 2, 31]])
